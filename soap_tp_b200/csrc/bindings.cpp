@@ -1,0 +1,89 @@
+// Python bindings of the native library (module soap_tp_b200._C).
+//
+// The reference exposes two pybind11 modules that take raw integer addresses plus leading dimensions
+// and release the GIL (src/soap_tp/csrc/slate_bindings.cpp:317-389, elpa_bindings.cpp:200-236).  The
+// same calling convention is used here: tensors are passed as data_ptr() integers with explicit
+// pitches, the CUDA stream as its integer handle.  Nothing here allocates device memory.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstdint>
+
+#include "comm.h"
+#include "elementwise.h"
+#include "gemm.h"
+
+namespace py = pybind11;
+using namespace soapb200;
+
+namespace {
+template <class T>
+T* ptr(uint64_t address) {
+  return reinterpret_cast<T*>(static_cast<uintptr_t>(address));
+}
+cudaStream_t stream_of(uint64_t handle) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(handle)); }
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "sm_100a kernels of soap_tp_b200";
+  m.def("compiled_gpu_backend", [] { return "cuda"; });
+  m.def("compiled_arch", [] { return "sm_100a"; });
+
+  m.def(
+      "gemm_tf32x3",
+      [](uint64_t a_hi, uint64_t a_lo, int64_t lda, uint64_t b_hi, uint64_t b_lo, int64_t ldb, int M, int N, int K,
+         int mode, int symmetric, int force_narrow, float alpha, float beta, uint64_t C, int64_t ldc, uint64_t Chi,
+         uint64_t Clo, int64_t ldp, uint64_t mom, uint64_t var, int64_t ldm, int64_t ldv, float beta1, float beta2,
+         float eps, float inv_bc1, float inv_sqrt_bc2, uint64_t status, uint64_t stream) {
+        GemmOperands ops{ptr<const float>(a_hi), ptr<const float>(a_lo), lda,
+                         ptr<const float>(b_hi), ptr<const float>(b_lo), ldb};
+        GemmProblem prob{};
+        prob.M = M; prob.N = N; prob.K = K;
+        prob.mode = mode; prob.symmetric = symmetric; prob.force_narrow = force_narrow;
+        prob.alpha = alpha; prob.beta = beta;
+        prob.C = ptr<float>(C); prob.ldc = ldc;
+        prob.Chi = ptr<float>(Chi); prob.Clo = ptr<float>(Clo); prob.ldp = ldp;
+        prob.mom = ptr<float>(mom); prob.var = ptr<float>(var); prob.ldm = ldm; prob.ldv = ldv;
+        prob.beta1 = beta1; prob.beta2 = beta2; prob.eps = eps;
+        prob.inv_bc1 = inv_bc1; prob.inv_sqrt_bc2 = inv_sqrt_bc2;
+        py::gil_scoped_release release;
+        gemm_tf32x3(ops, prob, ptr<int>(status), stream_of(stream));
+      },
+      "3xTF32 tcgen05 GEMM acc[m,n] = sum_k Za[k,m] Zb[k,n] with fused epilogue");
+
+  m.def("gemm_simt",
+        [](uint64_t A, int64_t a_sk, int64_t a_sm, uint64_t B, int64_t b_sk, int64_t b_sn, uint64_t C, int64_t c_sm,
+           int64_t c_sn, int M, int N, int K, float alpha, float beta, uint64_t stream) {
+          py::gil_scoped_release release;
+          gemm_simt(ptr<const float>(A), a_sk, a_sm, ptr<const float>(B), b_sk, b_sn, ptr<float>(C), c_sm, c_sn, M, N,
+                    K, alpha, beta, stream_of(stream));
+        });
+
+  m.def("adam_update",
+        [](uint64_t g, int64_t ldg, uint64_t mo, int64_t ldm, uint64_t v, int64_t ldv, uint64_t u, int64_t ldu, int rows,
+           int cols, float beta1, float beta2, float eps, float inv_bc1, float inv_sqrt_bc2, uint64_t stream) {
+          adam_update(ptr<const float>(g), ldg, ptr<float>(mo), ldm, ptr<float>(v), ldv, ptr<float>(u), ldu, rows, cols,
+                      beta1, beta2, eps, inv_bc1, inv_sqrt_bc2, stream_of(stream));
+        });
+
+  m.def("split_planes",
+        [](uint64_t src, int64_t s_i, int64_t s_j, uint64_t hi, uint64_t lo, int64_t ldo, int rows, int cols,
+           float scale, int nearest, uint64_t stream) {
+          split_planes(ptr<const float>(src), s_i, s_j, ptr<float>(hi), ptr<float>(lo), ldo, rows, cols, scale, nearest,
+                       stream_of(stream));
+        });
+
+  m.def("column_dot",
+        [](uint64_t a, int64_t lda, uint64_t b, int64_t ldb, uint64_t out, int rows, int cols, uint64_t stream) {
+          column_dot(ptr<const float>(a), lda, ptr<const float>(b), ldb, ptr<float>(out), rows, cols, stream_of(stream));
+        });
+
+  m.def("gather2d",
+        [](uint64_t src, int64_t s_i, int64_t s_j, uint64_t dst, int64_t d_i, int64_t d_j, uint64_t row_map,
+           uint64_t col_map, int rows, int cols, uint64_t stream) {
+          gather2d(ptr<const float>(src), s_i, s_j, ptr<float>(dst), d_i, d_j, ptr<const int64_t>(row_map),
+                   ptr<const int64_t>(col_map), rows, cols, stream_of(stream));
+        });
+
+  register_comm(m);
+}

@@ -1,0 +1,52 @@
+// Host-side interface of the GEMM kernels (gemm_tf32x3.cu, gemm_simt.cu).
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace soapb200 {
+
+enum EpilogueMode : int {
+  kEpiStore = 0,     // C[m + n*ldc] = alpha*acc + beta*C   (EMA when beta != 0); optional symmetric mirror
+  kEpiSplit = 1,     // write alpha*acc as hi/lo planes (operand of the next GEMM); optional plain copy in C
+  kEpiAdam = 2,      // acc is the projected gradient: update momentum/variance, write the update as planes
+  kEpiRowMajor = 3,  // C[m*ldc + n] = alpha*acc (tensor-parallel shard output)
+};
+
+// Operand planes.  a_* is the K x M column-major matrix Za (pitch lda floats), b_* the K x N matrix Zb.
+struct GemmOperands {
+  const float* a_hi;
+  const float* a_lo;
+  int64_t lda;
+  const float* b_hi;
+  const float* b_lo;
+  int64_t ldb;
+};
+
+struct GemmProblem {
+  int M, N, K;
+  int mode;
+  int symmetric;     // A == B: compute tiles on/below the diagonal, mirror the rest (kEpiStore only)
+  int force_narrow;  // use 128-wide tiles regardless of the problem size
+  float alpha, beta;
+  float* C;
+  int64_t ldc;
+  float* Chi;
+  float* Clo;
+  int64_t ldp;
+  float* mom;
+  float* var;
+  int64_t ldm, ldv;
+  float beta1, beta2, eps, inv_bc1, inv_sqrt_bc2;
+};
+
+// acc[m, n] = sum_k Za[k, m] * Zb[k, n] on tcgen05 with 3xTF32 compensation, then the epilogue.
+// `status` is the device status word that bounded waits report to.
+void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream);
+
+// Same contraction in plain fp32 FMA on CUDA cores from unsplit operands with arbitrary strides:
+// acc[m, n] = sum_k A[k*a_sk + m*a_sm] * B[k*b_sk + n*b_sn];  C[m*c_sm + n*c_sn] = alpha*acc + beta*C.
+// Used as the in-tree numerical cross-check of the tensor-core kernel and for problems far below one tile.
+void gemm_simt(const float* A, int64_t a_sk, int64_t a_sm, const float* B, int64_t b_sk, int64_t b_sn, float* C,
+               int64_t c_sm, int64_t c_sn, int M, int N, int K, float alpha, float beta, cudaStream_t stream);
+
+}  // namespace soapb200

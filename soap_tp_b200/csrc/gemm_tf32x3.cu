@@ -1,0 +1,355 @@
+// C = op(A^T B) on 5th-generation tensor cores with 3xTF32 error compensation.
+//
+// Problem form ("TN"): operands are column-major matrices Za (K x M) and Zb (K x N), i.e. both are
+// K-contiguous, and the kernel forms acc[m, n] = sum_k Za[k, m] * Zb[k, n].  Every product of the
+// SOAP pipeline is brought to this form by the caller (bases are kept in both orientations), so
+// one kernel serves the rotations, the Gram updates and the power iteration.
+//
+// fp32-class accuracy on kind::tf32 hardware: each operand is supplied as two planes,
+// hi = x with the 13 low mantissa bits cleared and lo = x - hi, prepared once per operand by
+// split_planes_kernel (elementwise.cu).  Per 8-deep k-step the kernel issues three UMMAs,
+// lo*hi + hi*lo + hi*hi, into one fp32 TMEM accumulator; the dropped lo*lo term is 2^-22 relative.
+//
+// Structure (one 128 x BN output tile per CTA, 192 threads):
+//   warp 0, one lane : TMA producer  - four 128-byte-swizzled boxes per stage (A hi/lo, B hi/lo)
+//   warp 1, one lane : MMA issuer    - tcgen05.mma.cta_group::1.kind::tf32, commit -> stage empty
+//   warps 2..5       : epilogue      - tcgen05.ld 32x32b, fused store / EMA / Adam / split / mirror
+// TMA zero-fills out-of-range rows and the K tail, so arbitrary M, N, K are handled by masking the
+// stores only.  All waits are bounded (ptx.cuh).
+//
+// Replaces the SLATE gemm calls of the reference (src/soap_tp/csrc/slate_bindings.cpp:55-123 and
+// :191-277), which run batched cuBLAS SGEMM on 128^3 tiles with MPI tile broadcasts in between.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <tuple>
+
+#include "gemm.h"
+#include "ptx.cuh"
+
+namespace soapb200 {
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 32;          // 32 fp32 = one 128-byte swizzle row
+constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each owning half of the tile's columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
+// The tensor core adds into its fp32 accumulator with truncation, so an accumulation that runs over
+// the whole K extent drifts linearly in K (measured 6e-5 relative at K = 8192).  The accumulator is
+// therefore drained every kPromote k-blocks: the epilogue warps add it, round-to-nearest, into a
+// running sum held in registers while the tensor core fills the other TMEM buffer.
+constexpr int kPromote = 2;      // k-blocks (of 32) accumulated inside TMEM before promotion
+
+template <int BN>
+struct TileConfig {
+  static constexpr int kStageBytes = 2 * (kBM + BN) * kBK * 4;
+  static constexpr int kStages = (BN == 256) ? 2 : 3;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (ping-pong)
+  static constexpr int kColsPerThread = BN / 2;
+};
+
+struct alignas(64) GemmMaps {
+  CUtensorMap a_hi, a_lo, b_hi, b_lo;
+};
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+template <int MODE>
+__device__ __forceinline__ void epilogue_element(const GemmProblem& prob, int m, int n, float acc) {
+  if constexpr (MODE == kEpiStore) {
+    float* dst = prob.C + m + static_cast<int64_t>(n) * prob.ldc;
+    float v = prob.alpha * acc;
+    if (prob.beta != 0.0f) v = fmaf(prob.beta, *dst, v);
+    *dst = v;
+    if (prob.symmetric && n < m) prob.C[n + static_cast<int64_t>(m) * prob.ldc] = v;
+  } else if constexpr (MODE == kEpiSplit) {
+    const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
+    const float v = prob.alpha * acc;
+    const float hi = tf32_round(v);
+    prob.Chi[off] = hi;
+    prob.Clo[off] = v - hi;
+    if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = v;
+  } else if constexpr (MODE == kEpiAdam) {
+    float* mp = prob.mom + m + static_cast<int64_t>(n) * prob.ldm;
+    float* vp = prob.var + m + static_cast<int64_t>(n) * prob.ldv;
+    const float g = acc;
+    const float mo = fmaf(prob.beta1, *mp, (1.0f - prob.beta1) * g);
+    const float va = fmaf(prob.beta2, *vp, (1.0f - prob.beta2) * g * g);
+    *mp = mo;
+    *vp = va;
+    const float u = (mo * prob.inv_bc1) / (sqrtf(va) * prob.inv_sqrt_bc2 + prob.eps);
+    const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
+    const float hi = tf32_round(u);
+    prob.Chi[off] = hi;
+    prob.Clo[off] = u - hi;
+    if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = g;
+  } else {  // kEpiRowMajor
+    prob.C[static_cast<int64_t>(m) * prob.ldc + n] = prob.alpha * acc;
+  }
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmProblem prob, int* status) {
+  using Cfg = TileConfig<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* acc_full = empty_bar + Cfg::kStages;   // [2] tensor core -> epilogue
+  uint64_t* acc_empty = acc_full + 2;              // [2] epilogue -> tensor core
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Grouped raster: GROUP tile-rows share their B panels in L2 while they sweep the tile columns.
+  const int tiles_m = (prob.M + kBM - 1) / kBM;
+  const int tiles_n = (prob.N + BN - 1) / BN;
+  constexpr int kGroup = 16;
+  int tile_m, tile_n;
+  {
+    const int per_group = kGroup * tiles_n;
+    const int group = blockIdx.x / per_group;
+    const int first_m = group * kGroup;
+    const int rows_in_group = min(kGroup, tiles_m - first_m);
+    const int within = blockIdx.x % per_group;
+    tile_m = first_m + within % rows_in_group;
+    tile_n = within / rows_in_group;
+  }
+  const int m0 = tile_m * kBM;
+  const int n0 = tile_n * BN;
+  // Symmetric products: tiles strictly above the diagonal are produced by mirroring.
+  if (prob.symmetric && n0 > m0 + kBM - 1) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], kEpiWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_descriptor(&maps.a_hi);
+    tma_prefetch_descriptor(&maps.a_lo);
+    tma_prefetch_descriptor(&maps.b_hi);
+    tma_prefetch_descriptor(&maps.b_lo);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int k_blocks = (prob.K + kBK - 1) / kBK;
+  const int chunks = (k_blocks + kPromote - 1) / kPromote;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      const int s = kb % Cfg::kStages;
+      const uint32_t round = kb / Cfg::kStages;
+      if (kb >= Cfg::kStages &&
+          !mbar_wait_bounded(&empty_bar[s], (round - 1) & 1, abort_flag, status, kStatusSlotWaitTimeout))
+        break;
+      uint8_t* stage = smem + s * Cfg::kStageBytes;
+      mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+      const int k0 = kb * kBK;
+      tma_load_2d(stage, &maps.a_hi, &full_bar[s], k0, m0);
+      tma_load_2d(stage + kBM * 128, &maps.a_lo, &full_bar[s], k0, m0);
+      tma_load_2d(stage + 2 * kBM * 128, &maps.b_hi, &full_bar[s], k0, n0);
+      tma_load_2d(stage + 2 * kBM * 128 + BN * 128, &maps.b_lo, &full_bar[s], k0, n0);
+    }
+    if (*abort_flag) {
+      // give copies that are still in flight time to land before the CTA's shared memory is released
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc = umma_idesc_tf32(kBM, BN);
+    bool ok = true;
+    int kb = 0;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int buf = c & 1;
+      if (c >= 2) {
+        ok = mbar_wait_bounded(&acc_empty[buf], ((c >> 1) - 1) & 1, abort_flag, status, kStatusAccumWaitTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * BN);
+      const int kb_end = min(k_blocks, kb + kPromote);
+      for (int first = 1; kb < kb_end; ++kb) {
+        const int s = kb % Cfg::kStages;
+        const uint32_t round = kb / Cfg::kStages;
+        ok = mbar_wait_bounded(&full_bar[s], round & 1, abort_flag, status, kStatusTmaWaitTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t stage = smem_u32(smem + s * Cfg::kStageBytes);
+        const uint64_t a_hi = umma_desc_kmajor_sw128(stage);
+        const uint64_t a_lo = umma_desc_kmajor_sw128(stage + kBM * 128);
+        const uint64_t b_hi = umma_desc_kmajor_sw128(stage + 2 * kBM * 128);
+        const uint64_t b_lo = umma_desc_kmajor_sw128(stage + 2 * kBM * 128 + BN * 128);
+#pragma unroll
+        for (int k = 0; k < kBK / 8; ++k) {
+          const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);  // 8 tf32 = 32 bytes along the swizzle row
+          // small terms first, the dominant hi*hi product last
+          umma_tf32_ss(tmem_acc, a_lo + adv, b_hi + adv, idesc, first ? 0u : 1u);
+          first = 0;
+          umma_tf32_ss(tmem_acc, a_hi + adv, b_lo + adv, idesc, 1);
+          umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+        }
+        umma_commit(&empty_bar[s]);  // stage reusable once these UMMAs have read it
+      }
+      if (ok) umma_commit(&acc_full[buf]);
+    }
+  } else if (warp >= 2) {
+    // ---------------- promotion + epilogue ----------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;              // TMEM lane quarter this warp may read
+    const int half = ew >> 2;                  // which half of the tile's columns
+    constexpr int kCols = Cfg::kColsPerThread;
+    const int col0 = half * kCols;
+    const int m = m0 + quarter * 32 + lane;
+    float sum[kCols];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) sum[j] = 0.0f;
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int buf = c & 1;
+      ok = mbar_wait_bounded(&acc_full[buf], (c >> 1) & 1, abort_flag, status, kStatusAccumWaitTimeout);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(buf * BN + col0);
+#pragma unroll
+      for (int cc = 0; cc < kCols; cc += 32) {
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + static_cast<uint32_t>(cc), raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[cc + j] += __uint_as_float(raw[j]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (ok && m < prob.M) {
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) {
+        const int n = n0 + col0 + j;
+        if (n < prob.N && !(prob.symmetric && n > m)) epilogue_element<MODE>(prob, m, n, sum[j]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor maps (driver entry point fetched at run time, so no link-time libcuda) and launch.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query);
+    if (err != cudaSuccess || query != cudaDriverEntryPointSuccess || ptr == nullptr)
+      throw std::runtime_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// K-contiguous fp32 matrix [rows][K] with row pitch ld (floats); box = 32 floats x box_rows rows.
+CUtensorMap make_operand_map(const float* base, int64_t K, int64_t rows, int64_t ld, int box_rows) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) throw std::invalid_argument("operand plane must be 16-byte aligned");
+  if ((ld * 4) % 16 != 0) throw std::invalid_argument("operand plane pitch must be a multiple of 4 floats");
+  CUtensorMap map;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
+                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(res));
+  return map;
+}
+
+template <int BN, int MODE>
+void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
+  using Cfg = TileConfig<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Cfg::kSmemBytes);
+    if (err != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
+    configured = true;
+  }
+  GemmMaps maps;
+  maps.a_hi = make_operand_map(ops.a_hi, prob.K, prob.M, ops.lda, kBM);
+  maps.a_lo = make_operand_map(ops.a_lo, prob.K, prob.M, ops.lda, kBM);
+  maps.b_hi = make_operand_map(ops.b_hi, prob.K, prob.N, ops.ldb, BN);
+  maps.b_lo = make_operand_map(ops.b_lo, prob.K, prob.N, ops.ldb, BN);
+  const int tiles_m = (prob.M + kBM - 1) / kBM;
+  const int tiles_n = (prob.N + BN - 1) / BN;
+  gemm_tf32x3_kernel<BN, MODE><<<tiles_m * tiles_n, kThreads, Cfg::kSmemBytes, stream>>>(maps, prob, status);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) throw std::runtime_error(std::string("gemm_tf32x3 launch: ") + cudaGetErrorString(err));
+}
+
+}  // namespace
+
+void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
+  if (prob.M <= 0 || prob.N <= 0) return;
+  if (prob.K <= 0) throw std::invalid_argument("gemm_tf32x3 needs K >= 1");
+  // Wide tiles when there are enough of them to fill the 148 SMs; narrower tiles otherwise.
+  const int64_t wide_tiles = static_cast<int64_t>((prob.M + kBM - 1) / kBM) * ((prob.N + 255) / 256);
+  const bool wide = prob.N > 128 && wide_tiles >= 148 && !prob.force_narrow;
+  switch (prob.mode) {
+    case kEpiStore:
+      wide ? launch<256, kEpiStore>(ops, prob, status, stream) : launch<128, kEpiStore>(ops, prob, status, stream);
+      break;
+    case kEpiSplit:
+      wide ? launch<256, kEpiSplit>(ops, prob, status, stream) : launch<128, kEpiSplit>(ops, prob, status, stream);
+      break;
+    case kEpiAdam:
+      wide ? launch<256, kEpiAdam>(ops, prob, status, stream) : launch<128, kEpiAdam>(ops, prob, status, stream);
+      break;
+    case kEpiRowMajor:
+      wide ? launch<256, kEpiRowMajor>(ops, prob, status, stream) : launch<128, kEpiRowMajor>(ops, prob, status, stream);
+      break;
+    default:
+      throw std::invalid_argument("gemm_tf32x3: unknown epilogue mode");
+  }
+}
+
+}  // namespace soapb200

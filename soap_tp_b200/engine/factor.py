@@ -1,0 +1,27 @@
+"""Dense factorisations on one GPU: Householder QR and the symmetric eigensolver.
+
+These operate on column-major device matrices that are entirely local (grid (1, 1), or a panel a
+rank has gathered).  See ``csrc/qr.cu`` and ``csrc/jacobi.cu`` for the kernels.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import kernels as k
+
+
+def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = None) -> Tensor:
+    """``Q <- explicit orthogonal factor of matrix[:, column_order]``; ``matrix`` is scratch."""
+    from . import qr
+
+    return qr.householder_qr(matrix, Q, column_order)
+
+
+def symmetric_eigenbasis(P: Tensor, Q: Tensor, work: Tensor, values: Tensor, implementation: str) -> Tensor:
+    """Eigenvectors of symmetric ``P`` into ``Q`` and eigenvalues into ``values``, both descending."""
+    from . import jacobi
+
+    return jacobi.symmetric_eigenbasis(P, Q, work, values)

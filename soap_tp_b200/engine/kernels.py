@@ -1,0 +1,242 @@
+"""Python wrappers of the native kernels (module ``soap_tp_b200._C``).
+
+Everything here launches this package's own sm_100a kernels on the current CUDA stream; there is
+no eager-PyTorch fallback.  If the extension is missing it is built in place
+(``soap_tp_b200.build_ext``); if that fails the import error propagates -- a CUDA tensor never
+silently takes another path.
+"""
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+from torch import Tensor
+
+try:
+    from .. import _C  # type: ignore[attr-defined]
+except ImportError:  # pragma: no cover - build on first use
+    from .. import build_ext
+
+    build_ext.build()
+    from .. import _C  # type: ignore[attr-defined]
+
+EPI_STORE, EPI_SPLIT, EPI_ADAM, EPI_ROW_MAJOR = 0, 1, 2, 3
+
+STATUS_MESSAGES = {
+    1: "GEMM consumer timed out waiting for a TMA stage",
+    2: "GEMM producer timed out waiting for a free stage",
+    3: "GEMM epilogue timed out waiting for the accumulator",
+    4: "cross-rank barrier timed out",
+    5: "bad kernel argument",
+}
+
+LAUNCH_COUNTS: Dict[str, int] = {}
+
+
+def _count(name: str) -> None:
+    LAUNCH_COUNTS[name] = LAUNCH_COUNTS.get(name, 0) + 1
+
+
+def total_launches() -> int:
+    """Number of kernels of this library launched by this process so far."""
+    return sum(LAUNCH_COUNTS.values())
+
+
+class SoapKernelError(RuntimeError):
+    """A kernel of this library reported a bounded-wait timeout or a bad argument."""
+
+
+_STATUS: Dict[int, Tensor] = {}
+
+
+def status_word(device: torch.device) -> Tensor:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _STATUS.get(index)
+    if word is None:
+        word = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", index))
+        _STATUS[index] = word
+    return word
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise :class:`SoapKernelError` if any kernel gave up on a wait."""
+    words = _STATUS.items() if device is None else [(device.index or 0, status_word(device))]
+    for index, word in list(words):
+        code = int(word[0].item())
+        if code != 0:
+            word.zero_()
+            raise SoapKernelError(f"cuda:{index}: {STATUS_MESSAGES.get(code, f'status {code}')}")
+
+
+def mark_written(*tensors: Optional[Tensor]) -> None:
+    """Bump the version counter of tensors a kernel wrote through a raw pointer, so that caches
+    keyed on ``tensor._version`` (basis planes) notice the change."""
+    for tensor in tensors:
+        if tensor is not None:
+            torch.autograd.graph.increment_version(tensor)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+@dataclass
+class Planes:
+    """hi/lo planes of a K x cols column-major operand (``hi + lo`` reproduces the fp32 values)."""
+
+    hi: Tensor
+    lo: Tensor
+    depth: int   # K: the contiguous, contracted extent
+    cols: int
+    ld: int
+
+    @staticmethod
+    def empty(depth: int, cols: int, device) -> "Planes":
+        ld = max(4, round_up(depth, 4))
+        storage = torch.empty((2, max(1, cols), ld), dtype=torch.float32, device=device)
+        return Planes(storage[0], storage[1], depth, cols, ld)
+
+    def dense(self) -> Tensor:
+        """The represented K x cols matrix (for tests)."""
+        return (self.hi[: self.cols, : self.depth] + self.lo[: self.cols, : self.depth]).T
+
+
+SPLIT_ROUND_NEAREST = os.environ.get("SOAP_TP_SPLIT_NEAREST", "1") == "1"
+
+
+def split_planes(source: Tensor, *, transpose: bool = False, out: Optional[Planes] = None, scale: float = 1.0,
+                 nearest: Optional[bool] = None) -> Planes:
+    """Split a 2-D fp32 tensor (any strides) into operand planes.
+
+    The operand is ``source`` itself (``depth = rows``) or, with ``transpose=True``, its transpose.
+    """
+    if source.dtype != torch.float32:
+        source = source.float()
+    rows, cols = source.shape
+    s_i, s_j = source.stride()
+    if transpose:
+        rows, cols, s_i, s_j = cols, rows, s_j, s_i
+    if out is None:
+        out = Planes.empty(rows, cols, source.device)
+    assert out.depth == rows and out.cols == cols
+    _C.split_planes(source.data_ptr(), s_i, s_j, out.hi.data_ptr(), out.lo.data_ptr(), out.ld, rows, cols,
+                    float(scale), int(SPLIT_ROUND_NEAREST if nearest is None else nearest), _stream())
+    _count("split_planes_kernel")
+    return out
+
+
+def gemm(
+    a: Planes,
+    b: Planes,
+    *,
+    mode: int = EPI_STORE,
+    out: Optional[Tensor] = None,
+    out_ld: Optional[int] = None,
+    out_planes: Optional[Planes] = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    symmetric: bool = False,
+    momentum: Optional[Tensor] = None,
+    variance: Optional[Tensor] = None,
+    adam: Optional[dict] = None,
+    force_narrow: bool = False,
+) -> None:
+    """``acc[m, n] = sum_k a[k, m] * b[k, n]`` then the fused epilogue (see ``csrc/gemm.h``).
+
+    ``out`` is a column-major ``M x N`` view for ``EPI_STORE`` (and the optional plain copy of
+    ``EPI_SPLIT``/``EPI_ADAM``) or a row-major ``M x N`` tensor for ``EPI_ROW_MAJOR``.
+    """
+    assert a.depth == b.depth, (a.depth, b.depth)
+    M, N, K = a.cols, b.cols, a.depth
+    if M == 0 or N == 0:
+        return
+    c_ptr, ldc = 0, 0
+    if out is not None:
+        c_ptr = out.data_ptr()
+        if mode == EPI_ROW_MAJOR:
+            assert out.stride(1) == 1 or out.shape[1] == 1
+            ldc = out.stride(0) if out.shape[0] > 1 else max(1, out.shape[1])
+        else:
+            assert out.stride(0) == 1 or out.shape[0] == 1
+            ldc = out_ld if out_ld is not None else (out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0]))
+    chi = clo = ldp = 0
+    if out_planes is not None:
+        assert out_planes.depth == M and out_planes.cols == N
+        chi, clo, ldp = out_planes.hi.data_ptr(), out_planes.lo.data_ptr(), out_planes.ld
+    mom = var = ldm = ldv = 0
+    b1 = b2 = eps = ibc1 = isbc2 = 0.0
+    if mode == EPI_ADAM:
+        assert momentum is not None and variance is not None and adam is not None and out_planes is not None
+        mom, var = momentum.data_ptr(), variance.data_ptr()
+        ldm = momentum.stride(1) if momentum.shape[1] > 1 else max(1, momentum.shape[0])
+        ldv = variance.stride(1) if variance.shape[1] > 1 else max(1, variance.shape[0])
+        b1, b2, eps = adam["beta1"], adam["beta2"], adam["eps"]
+        ibc1, isbc2 = 1.0 / adam["bias_correction1"], 1.0 / math.sqrt(adam["bias_correction2"])
+    status = status_word(a.hi.device)
+    _C.gemm_tf32x3(a.hi.data_ptr(), a.lo.data_ptr(), a.ld, b.hi.data_ptr(), b.lo.data_ptr(), b.ld, M, N, K,
+                   mode, int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
+                   mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, status.data_ptr(), _stream())
+    mark_written(out, momentum, variance)
+    _count("gemm_tf32x3_kernel")
+
+
+def gemm_simt(a: Tensor, b: Tensor, out: Tensor, *, alpha: float = 1.0, beta: float = 0.0) -> Tensor:
+    """``out[m, n] = alpha * sum_k a[k, m] * b[k, n] + beta * out`` in fp32 FMA (any strides)."""
+    K, M = a.shape
+    K2, N = b.shape
+    assert K == K2 and out.shape == (M, N)
+    _C.gemm_simt(a.data_ptr(), a.stride(0), a.stride(1), b.data_ptr(), b.stride(0), b.stride(1), out.data_ptr(),
+                 out.stride(0), out.stride(1), M, N, K, float(alpha), float(beta), _stream())
+    _count("gemm_simt_kernel")
+    return out
+
+
+def _ld(t: Tensor) -> int:
+    return t.stride(1) if t.shape[1] > 1 else max(1, t.shape[0])
+
+
+def adam_update(gradient: Tensor, momentum: Tensor, variance: Tensor, beta1: float, beta2: float, eps: float,
+                bias_correction1: float, bias_correction2: float) -> Tensor:
+    """Fused Adam on 2-D tensors; the result has the strides of ``variance``."""
+    for t in (gradient, momentum, variance):
+        if t.dtype != torch.float32 or t.ndim != 2:
+            raise ValueError("adam_update on CUDA needs 2-D float32 tensors.")
+    update = torch.empty_strided(variance.shape, variance.stride(), dtype=torch.float32, device=variance.device)
+    rows, cols = variance.shape
+    views = [gradient, momentum, variance, update]
+    if not all(v.stride(0) == 1 or v.shape[0] == 1 for v in views):
+        if all(v.stride(1) == 1 or v.shape[1] == 1 for v in views):
+            views = [v.T for v in views]
+            rows, cols = cols, rows
+        else:
+            raise ValueError("adam_update needs all operands column-major or all row-major.")
+    g, m, v, u = views
+    _C.adam_update(g.data_ptr(), _ld(g), m.data_ptr(), _ld(m), v.data_ptr(), _ld(v), u.data_ptr(), _ld(u), rows, cols,
+                   beta1, beta2, eps, 1.0 / bias_correction1, 1.0 / math.sqrt(bias_correction2), _stream())
+    _count("adam_kernel")
+    return update
+
+
+def column_dot(a: Tensor, b: Tensor, rows: int, cols: int, out: Optional[Tensor] = None) -> Tensor:
+    if out is None:
+        out = torch.empty(cols, dtype=torch.float32, device=a.device)
+    _C.column_dot(a.data_ptr(), _ld(a), b.data_ptr(), _ld(b), out.data_ptr(), rows, cols, _stream())
+    _count("column_dot_kernel")
+    return out
+
+
+def gather2d(src: Tensor, dst: Tensor, row_map: Optional[Tensor], col_map: Optional[Tensor]) -> Tensor:
+    """``dst[i, j] = src[row_map[i], col_map[j]]`` (``None`` = identity); ``dst`` must not alias ``src``."""
+    rows, cols = dst.shape
+    _C.gather2d(src.data_ptr(), src.stride(0), src.stride(1), dst.data_ptr(), dst.stride(0), dst.stride(1),
+                row_map.data_ptr() if row_map is not None else 0, col_map.data_ptr() if col_map is not None else 0,
+                rows, cols, _stream())
+    _count("gather2d_kernel")
+    return dst

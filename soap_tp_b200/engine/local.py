@@ -1,0 +1,227 @@
+"""Single-GPU (grid (1, 1)) device pipeline.
+
+With one rank the packed block-cyclic buffers ARE the dense column-major matrices, so the whole
+step is a chain of this package's kernels on one stream:
+
+    split G (both orientations)                                   split_planes_kernel x2
+    T   = X^T Q_L                (planes)                          gemm_tf32x3 / split epilogue
+    Y   = T^T Q_R, Adam(Y) -> U  (planes), m, v updated in place   gemm_tf32x3 / Adam epilogue
+    T2  = U^T Q_L^T              (planes)                          gemm_tf32x3 / split epilogue
+    out = T2^T Q_R^T             (row-major shard)                 gemm_tf32x3 / row-major epilogue
+    L   = b L + (1-b) G G^T,  R = b R + (1-b) G^T G                gemm_tf32x3 / EMA epilogue, lower tiles + mirror
+
+Every product is brought to the kernel's single form ``acc = Za^T Zb`` with K-contiguous operands
+by keeping each basis in both orientations as hi/lo planes; the planes are rebuilt only when the
+basis tensor changes (refresh, initialisation, or a user writing into ``state``).
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from typing import Any, Dict, MutableMapping, Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import kernels as k
+from . import factor
+
+
+class BasisPlanes:
+    """Both orientations of one orthogonal basis as operand planes, tied to a tensor version."""
+
+    def __init__(self) -> None:
+        self.key: Optional[tuple] = None
+        self.plain: Optional[k.Planes] = None       # operand Q   (depth = rows of Q)
+        self.transposed: Optional[k.Planes] = None  # operand Q^T (depth = cols of Q)
+
+    def refresh(self, Q: Tensor, size: int) -> None:
+        key = (Q.data_ptr(), Q._version, size)
+        if key == self.key:
+            return
+        view = Q[:size, :size]
+        self.plain = k.split_planes(view, out=self.plain)
+        self.transposed = k.split_planes(view, transpose=True, out=self.transposed)
+        self.key = (Q.data_ptr(), Q._version, size)
+
+
+class ParameterContext:
+    """Per-parameter device-side caches (basis planes)."""
+
+    def __init__(self) -> None:
+        self.left = BasisPlanes()
+        self.right = BasisPlanes()
+
+
+_CONTEXTS: "OrderedDict[int, ParameterContext]" = OrderedDict()
+_WORKSPACES: Dict[tuple, Any] = {}
+
+
+def context_for(state: MutableMapping[str, Any]) -> ParameterContext:
+    key = state["left_basis"].data_ptr()
+    ctx = _CONTEXTS.get(key)
+    if ctx is None:
+        ctx = ParameterContext()
+        _CONTEXTS[key] = ctx
+        while len(_CONTEXTS) > 4096:
+            _CONTEXTS.popitem(last=False)
+    return ctx
+
+
+def workspace_planes(tag: str, depth: int, cols: int, device) -> k.Planes:
+    """Scratch operand planes shared by every parameter of the same shape on ``device``."""
+    key = (tag, depth, cols, str(device))
+    planes = _WORKSPACES.get(key)
+    if planes is None:
+        planes = k.Planes.empty(depth, cols, device)
+        _WORKSPACES[key] = planes
+    return planes
+
+
+def workspace_matrix(tag: str, rows: int, cols: int, device) -> Tensor:
+    key = ("m", tag, rows, cols, str(device))
+    matrix = _WORKSPACES.get(key)
+    if matrix is None:
+        matrix = torch.empty((max(1, cols), max(1, rows)), dtype=torch.float32, device=device).T
+        _WORKSPACES[key] = matrix
+    return matrix
+
+
+def release_workspaces() -> None:
+    _WORKSPACES.clear()
+    _CONTEXTS.clear()
+
+
+def _gradient_planes(gradient: Tensor, rows: int, cols: int) -> Tuple[k.Planes, k.Planes]:
+    """Planes of G (depth = rows) and of G^T (depth = cols) from the row-major gradient."""
+    g32 = gradient.detach()
+    if g32.dtype != torch.float32:
+        g32 = g32.float()
+    device = g32.device
+    xp = k.split_planes(g32, out=workspace_planes("X", rows, cols, device))
+    gtp = k.split_planes(g32, transpose=True, out=workspace_planes("GT", cols, rows, device))
+    return xp, gtp
+
+
+def rotate_planes(source: k.Planes, first: k.Planes, second: k.Planes, rows: int, cols: int, device, *, tag: str,
+                  **final) -> None:
+    """``final epilogue( (source^T first)^T second )`` -- two chained GEMMs through scratch planes."""
+    middle = workspace_planes(tag, source.cols, first.cols, device)
+    k.gemm(source, first, mode=k.EPI_SPLIT, out_planes=middle)
+    k.gemm(middle, second, **final)
+
+
+def gram_updates(xp: k.Planes, gtp: k.Planes, state, beta: float, rows: int, cols: int) -> None:
+    k.gemm(gtp, gtp, out=state["left_preconditioner"][:rows, :rows], alpha=1.0 - beta, beta=beta, symmetric=True)
+    k.gemm(xp, xp, out=state["right_preconditioner"][:cols, :cols], alpha=1.0 - beta, beta=beta, symmetric=True)
+
+
+def soap_step(
+    gradient: Tensor,
+    state: MutableMapping[str, Any],
+    *,
+    global_shape,
+    beta: float,
+    beta1: float,
+    beta2: float,
+    eps: float,
+    interval: int,
+    implementation: str,
+    initializing: bool,
+) -> Tensor:
+    rows, cols = global_shape
+    device = gradient.device
+    xp, gtp = _gradient_planes(gradient.reshape(rows, cols), rows, cols)
+    if initializing:
+        gram_updates(xp, gtp, state, beta, rows, cols)
+        for side, size in (("left", rows), ("right", cols)):
+            values = torch.empty(size, dtype=torch.float32, device=device)
+            factor.symmetric_eigenbasis(
+                state[f"{side}_preconditioner"][:size, :size], state[f"{side}_basis"][:size, :size],
+                state[f"{side}_work"][:size, :size], values, implementation,
+            )
+        state["step"] = 0
+        return torch.zeros((rows, cols), dtype=torch.float32, device=device)
+
+    step = int(state["step"]) + 1
+    ctx = context_for(state)
+    ctx.left.refresh(state["left_basis"], rows)
+    ctx.right.refresh(state["right_basis"], cols)
+    bias2 = 1.0 - beta2**step
+    adam = dict(beta1=beta1, beta2=beta2, eps=eps / math.sqrt(bias2),
+                bias_correction1=1.0 - beta1**step, bias_correction2=bias2)
+    up = workspace_planes("U", rows, cols, device)
+    rotate_planes(xp, ctx.left.plain, ctx.right.plain, rows, cols, device, tag="T",
+                  mode=k.EPI_ADAM, out_planes=up, momentum=state["momentum"][:rows, :cols],
+                  variance=state["variance"][:rows, :cols], adam=adam)
+    update = torch.empty((rows, cols), dtype=torch.float32, device=device)
+    rotate_planes(up, ctx.left.transposed, ctx.right.transposed, rows, cols, device, tag="T",
+                  mode=k.EPI_ROW_MAJOR, out=update)
+    gram_updates(xp, gtp, state, beta, rows, cols)
+    if step % interval == 0:
+        refresh(state, global_shape)
+    state["step"] = step
+    return update
+
+
+def rotate(matrix: Tensor, Q_left: Tensor, Q_right: Tensor, global_shape, direction: str) -> Tensor:
+    rows, cols = global_shape
+    device = matrix.device
+    left, right = BasisPlanes(), BasisPlanes()
+    left.refresh(Q_left, rows)
+    right.refresh(Q_right, cols)
+    view = matrix[:rows, :cols]
+    source = k.split_planes(view, out=workspace_planes("X", rows, cols, device))
+    if direction == "forward":
+        rotate_planes(source, left.plain, right.plain, rows, cols, device, tag="T", mode=k.EPI_STORE, out=view)
+    else:
+        rotate_planes(source, left.transposed, right.transposed, rows, cols, device, tag="T", mode=k.EPI_STORE, out=view)
+    return matrix
+
+
+def estimated_order(P: Tensor, Q: Tensor, work: Tensor, size: int) -> Tensor:
+    """``work <- P Q`` (P symmetric, so ``P^T Q``), estimates ``colsum(Q * work)``, stable descending order."""
+    device = P.device
+    pp = k.split_planes(P[:size, :size], out=workspace_planes("P", size, size, device))
+    qp = k.split_planes(Q[:size, :size], out=workspace_planes("Qtmp", size, size, device))
+    k.gemm(pp, qp, out=work[:size, :size])
+    estimates = k.column_dot(Q, work, size, size)
+    return torch.argsort(estimates, descending=True, stable=True)
+
+
+def power_iteration_qr(P: Tensor, Q: Tensor, work: Tensor, size: int) -> Tensor:
+    order = estimated_order(P, Q, work, size)
+    factor.householder_qr(work[:size, :size], Q[:size, :size], column_order=order)
+    return order
+
+
+def permute(matrix: Tensor, global_shape, row_order: Tensor, column_order: Tensor) -> Tensor:
+    rows, cols = global_shape
+    scratch = workspace_matrix("perm", rows, cols, matrix.device)
+    view = matrix[:rows, :cols]
+    k.gather2d(view, scratch, row_order, column_order)
+    view.copy_(scratch)
+    return matrix
+
+
+def refresh(state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tensor]:
+    """Power iteration + QR on both sides with momentum transport and variance permutation."""
+    rows, cols = global_shape
+    momentum, variance = state["momentum"], state["variance"]
+    device = momentum.device
+    ctx = context_for(state)
+    ctx.left.refresh(state["left_basis"], rows)
+    ctx.right.refresh(state["right_basis"], cols)
+    # momentum out of the old bases: Q_L M Q_R^T, kept as planes for the way back
+    mp = k.split_planes(momentum[:rows, :cols], out=workspace_planes("X", rows, cols, device))
+    parameter_space = workspace_planes("U", rows, cols, device)
+    rotate_planes(mp, ctx.left.transposed, ctx.right.transposed, rows, cols, device, tag="T",
+                  mode=k.EPI_SPLIT, out_planes=parameter_space)
+    left_order = power_iteration_qr(state["left_preconditioner"], state["left_basis"], state["left_work"], rows)
+    right_order = power_iteration_qr(state["right_preconditioner"], state["right_basis"], state["right_work"], cols)
+    permute(variance, global_shape, left_order, right_order)
+    ctx.left.refresh(state["left_basis"], rows)
+    ctx.right.refresh(state["right_basis"], cols)
+    rotate_planes(parameter_space, ctx.left.plain, ctx.right.plain, rows, cols, device, tag="T",
+                  mode=k.EPI_STORE, out=momentum[:rows, :cols])
+    return left_order, right_order
