@@ -8,7 +8,7 @@ namespace soapb200 {
 enum EpilogueMode : int {
   kEpiStore = 0,     // C[m + n*ldc] = alpha*acc + beta*C   (EMA when beta != 0); optional symmetric mirror
   kEpiSplit = 1,     // write alpha*acc as hi/lo planes (operand of the next GEMM); optional plain copy in C
-  kEpiAdam = 2,      // acc is the projected gradient: update momentum/variance, write the update as planes
+  kEpiAdam = 2,      // acc is the projected gradient: update momentum/variance; update -> planes and/or C
   kEpiRowMajor = 3,  // C[m*ldc + n] = alpha*acc (tensor-parallel shard output)
 };
 

@@ -89,11 +89,13 @@ __device__ __forceinline__ void epilogue_element(const GemmProblem& prob, int m,
     *mp = mo;
     *vp = va;
     const float u = (mo * prob.inv_bc1) / (sqrtf(va) * prob.inv_sqrt_bc2 + prob.eps);
-    const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
-    const float hi = tf32_round(u);
-    prob.Chi[off] = hi;
-    prob.Clo[off] = u - hi;
-    if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = g;
+    if (prob.Chi) {
+      const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
+      const float hi = tf32_round(u);
+      prob.Chi[off] = hi;
+      prob.Clo[off] = u - hi;
+    }
+    if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = u;
   } else {  // kEpiRowMajor
     prob.C[static_cast<int64_t>(m) * prob.ldc + n] = prob.alpha * acc;
   }

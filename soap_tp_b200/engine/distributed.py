@@ -1,0 +1,497 @@
+"""Multi-GPU device pipeline on a ``Pr x Pc`` grid.
+
+Every distributed product is a stationary-C GEMM: a rank computes exactly the tiles of the result
+it owns in the packed block-cyclic layout.  For ``C = Za^T Zb`` it needs all K rows of the columns
+of ``Za`` that map to its local rows and of the columns of ``Zb`` that map to its local columns.
+Those two panels are PULLED from the peers' symmetric segments by ``dist_gather_kernel``
+(``csrc/comm.cu``): one kernel that reads the peers' memory over NVLink, reorders it into local
+column order and writes the hi/lo operand planes of the 3xTF32 GEMM -- the all-gather, the layout
+change (including the tensor-parallel shard -> block-cyclic redistribution of the gradient and the
+column permutation of the power iterate) and the operand split are one pass.  The GEMM then runs
+entirely on local memory and its epilogue writes either the packed state buffer (EMA, Adam) or the
+symmetric segment the next stage pulls from.  Panels of the bases are cached until the basis
+changes, so a steady step moves only gradient-sized panels.
+
+Ordering between ranks is one barrier per producer/consumer edge (see ``parallel/comm.py``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, MutableMapping, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from ..layout import grid_coords, numroc, owned_indices
+from ..parallel.comm import Communicator, SymmetricSegment, get_communicator
+from . import factor
+from . import kernels as k
+
+KIND_BLOCK_CYCLIC, KIND_ROW_SHARDS, KIND_COL_SHARDS = 0, 1, 2
+
+
+@dataclass
+class Source:
+    """A matrix spread over the ranks, addressable by every rank through a symmetric segment."""
+
+    segment: SymmetricSegment
+    kind: int
+    rows: int
+    cols: int
+    nb_r: int = 1
+    nb_c: int = 1
+    Pr: int = 1
+    Pc: int = 1
+    world: int = 1
+
+
+@dataclass
+class IndexMap:
+    p: int = 0
+    P: int = 1
+    nb: int = 1
+    offset: int = 0
+    perm: Optional[Tensor] = None
+
+
+IDENTITY = IndexMap()
+
+
+def dist_gather(src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, cols_out: int, *, transpose: bool = False,
+                planes: Optional[k.Planes] = None, out: Optional[Tensor] = None) -> None:
+    """``out(i, j) = src(map_i(i), map_j(j))`` (``src(map_j(j), map_i(i))`` if ``transpose``)."""
+    if rows_out <= 0 or cols_out <= 0:
+        return
+    if planes is not None:
+        hi, lo, d_i, d_j = planes.hi.data_ptr(), planes.lo.data_ptr(), 1, planes.ld
+    else:
+        assert out is not None
+        hi, lo = out.data_ptr(), 0
+        d_i = out.stride(0) if out.shape[0] > 1 else 1
+        d_j = out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0])
+    k._C.dist_gather(
+        src.segment.peer_table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
+        map_i.p, map_i.P, map_i.nb, map_i.offset, map_i.perm.data_ptr() if map_i.perm is not None else 0,
+        map_j.p, map_j.P, map_j.nb, map_j.offset, map_j.perm.data_ptr() if map_j.perm is not None else 0,
+        int(transpose), hi, lo, d_i, d_j, rows_out, cols_out, k._stream())
+    k._count("dist_gather_kernel")
+    if out is not None:
+        k.mark_written(out)
+
+
+def _packed_view(segment: SymmetricSegment, local_rows: int, local_cols: int) -> Tensor:
+    """Column-major ``local_rows x local_cols`` view (exact pitch) at the start of a segment."""
+    lr, lc = max(1, local_rows), max(1, local_cols)
+    return segment.local[: lr * lc].view(lc, lr).T
+
+
+class GridEngine:
+    """Distributed kernels' driver for one ``(device, grid, block_size)``."""
+
+    def __init__(self, device: torch.device, grid: Tuple[int, int], block_size: int) -> None:
+        self.comm: Communicator = get_communicator(device)
+        self.device = torch.device(device)
+        self.grid = grid
+        self.nb = block_size
+        self.Pr, self.Pc = grid
+        self.rank = self.comm.rank
+        self.world = self.comm.world
+        self.pr, self.pc = grid_coords(self.rank, grid)
+        self._planes: Dict[tuple, k.Planes] = {}
+        self._basis_cache: Dict[tuple, dict] = {}
+
+    # ---- small helpers -----------------------------------------------------------------------
+    def rows_of(self, n: int) -> int:
+        return numroc(n, self.nb, self.pr, self.Pr)
+
+    def cols_of(self, n: int) -> int:
+        return numroc(n, self.nb, self.pc, self.Pc)
+
+    def row_map(self, perm: Optional[Tensor] = None) -> IndexMap:
+        return IndexMap(self.pr, self.Pr, self.nb, 0, perm)
+
+    def col_map(self, perm: Optional[Tensor] = None) -> IndexMap:
+        return IndexMap(self.pc, self.Pc, self.nb, 0, perm)
+
+    def planes(self, tag: str, depth: int, cols: int) -> k.Planes:
+        key = (tag, depth, cols)
+        found = self._planes.get(key)
+        if found is None:
+            found = k.Planes.empty(depth, cols, self.device)
+            self._planes[key] = found
+        return found
+
+    def packed_segment(self, tag: str, shape) -> Tuple[SymmetricSegment, Tensor, Source]:
+        """Symmetric staging buffer holding a packed block-cyclic matrix of global ``shape``."""
+        rows, cols = shape
+        most_rows = numroc(rows, self.nb, 0, self.Pr)
+        most_cols = numroc(cols, self.nb, 0, self.Pc)
+        segment = self.comm.segment(f"{tag}:{rows}x{cols}:{self.nb}:{self.Pr}x{self.Pc}", max(1, most_rows) * max(1, most_cols))
+        view = _packed_view(segment, self.rows_of(rows), self.cols_of(cols))
+        return segment, view, Source(segment, KIND_BLOCK_CYCLIC, rows, cols, self.nb, self.nb, self.Pr, self.Pc, self.world)
+
+    def stage_packed(self, tag: str, matrix: Tensor, shape) -> Source:
+        """Copy this rank's packed buffer into the symmetric staging segment ``tag``."""
+        _, view, source = self.packed_segment(tag, shape)
+        lr, lc = self.rows_of(shape[0]), self.cols_of(shape[1])
+        if lr and lc:
+            k.gather2d(matrix[:lr, :lc], view[:lr, :lc], None, None)
+        return source
+
+    def stage_shard(self, shard: Tensor, global_shape, shard_dim: int) -> Source:
+        rows, cols = global_shape
+        segment = self.comm.segment(f"shard:{rows}x{cols}:{shard_dim}", max(1, shard.numel()))
+        flat = segment.local[: shard.numel()].view(shard.shape)
+        source = shard.detach()
+        if source.dtype != torch.float32 or not source.is_contiguous():
+            flat.copy_(source)
+        else:
+            k.gather2d(source, flat, None, None)
+        kind = KIND_ROW_SHARDS if shard_dim == 0 else KIND_COL_SHARDS
+        return Source(segment, kind, rows, cols, world=self.world)
+
+    # ---- cached panels of a basis -------------------------------------------------------------
+    def basis_panels(self, Q: Tensor, size: int, tag: str) -> Tuple[k.Planes, k.Planes]:
+        """Planes of ``Q[:, my column class]`` (depth = size) and of ``Q^T[:, my column class]``,
+        i.e. rows of ``Q`` in my column class.  Collective; cached on the tensor version."""
+        entry = self._basis_cache.setdefault((Q.data_ptr(), size), {})
+        # Ranks run the same program on the same step, so staleness is decided locally: a basis
+        # changes on all ranks (refresh, initialisation, checkpoint load) or on none.
+        if entry.get("key") == (Q._version, size):
+            return entry["plain"], entry["transposed"]
+        source = self.stage_packed("basis", Q, (size, size))
+        self.comm.barrier()
+        cols = self.cols_of(size)
+        plain = entry.get("plain") or k.Planes.empty(size, cols, self.device)
+        transposed = entry.get("transposed") or k.Planes.empty(size, cols, self.device)
+        dist_gather(source, IDENTITY, self.col_map(), size, cols, planes=plain)
+        dist_gather(source, IDENTITY, self.col_map(), size, cols, transpose=True, planes=transposed)
+        self.comm.barrier()
+        entry.update(key=(Q._version, size), plain=plain, transposed=transposed)
+        return plain, transposed
+
+    # ---- two chained stationary-C products ---------------------------------------------------
+    def two_sided(self, source: Source, shape, first: k.Planes, second: k.Planes, *, gathered: Optional[k.Planes] = None,
+                  **final) -> k.Planes:
+        """``final( (X^T F)^T S )`` for the ``rows x cols`` matrix ``X`` behind ``source``.
+
+        ``first`` holds ``F[:, my column class]`` (depth rows), ``second`` holds ``S[:, my column
+        class]`` (depth cols).  The caller has already ordered ``source`` before this call.  Returns
+        the gathered operand planes of ``X`` (``X[:, my row class]``) for reuse.
+        """
+        rows, cols = shape
+        a = gathered
+        if a is None:
+            a = self.planes("panel_a", rows, self.rows_of(cols))
+            dist_gather(source, IDENTITY, self.row_map(), rows, self.rows_of(cols), planes=a)
+        _, t_view, t_source = self.packed_segment("middle", (cols, rows))
+        k.gemm(a, first, mode=k.EPI_STORE, out=t_view[: max(1, a.cols), : max(1, first.cols)])
+        self.comm.barrier()
+        ta = self.planes("panel_t", cols, self.rows_of(rows))
+        dist_gather(t_source, IDENTITY, self.row_map(), cols, self.rows_of(rows), planes=ta)
+        k.gemm(ta, second, **final)
+        return a
+
+
+_ENGINES: Dict[tuple, GridEngine] = {}
+
+
+def engine_for(device: torch.device, grid, block_size: int) -> GridEngine:
+    key = (str(torch.device(device)), tuple(grid), int(block_size))
+    engine = _ENGINES.get(key)
+    if engine is None:
+        engine = GridEngine(device, tuple(grid), int(block_size))
+        _ENGINES[key] = engine
+    return engine
+
+
+def reset_engines() -> None:
+    _ENGINES.clear()
+
+
+# ---------------------------------------------------------------------------------------------
+# Public-op entry points (each is collective and self-contained)
+# ---------------------------------------------------------------------------------------------
+def redistribute_tp_to_bc(matrix: Tensor, global_shape, block_size: int, grid, shard_dim: int) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size)
+    rows, cols = global_shape
+    source = e.stage_shard(matrix, global_shape, shard_dim)
+    e.comm.barrier()
+    lr, lc = e.rows_of(rows), e.cols_of(cols)
+    packed = torch.empty((max(1, lc), max(1, lr)), dtype=torch.float32, device=matrix.device).T
+    dist_gather(source, e.row_map(), e.col_map(), lr, lc, out=packed)
+    e.comm.barrier()
+    return packed if matrix.dtype == torch.float32 else packed.to(matrix.dtype)
+
+
+def _pull_shard(e: GridEngine, source: Source, global_shape, shard_dim: int) -> Tensor:
+    rows, cols = global_shape
+    if shard_dim == 0:
+        per = rows // e.world
+        shard = torch.empty((per, cols), dtype=torch.float32, device=e.device)
+        dist_gather(source, IndexMap(offset=e.rank * per), IDENTITY, per, cols, out=shard)
+    else:
+        per = cols // e.world
+        shard = torch.empty((rows, per), dtype=torch.float32, device=e.device)
+        dist_gather(source, IDENTITY, IndexMap(offset=e.rank * per), rows, per, out=shard)
+    return shard
+
+
+def redistribute_bc_to_tp(matrix: Tensor, global_shape, block_size: int, grid, shard_dim: int) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size)
+    source = e.stage_packed("stage", matrix if matrix.dtype == torch.float32 else matrix.float(), global_shape)
+    e.comm.barrier()
+    shard = _pull_shard(e, source, global_shape, shard_dim)
+    e.comm.barrier()
+    return shard if matrix.dtype == torch.float32 else shard.to(matrix.dtype)
+
+
+def rotate(matrix: Tensor, Q_left: Tensor, Q_right: Tensor, global_shape, block_size: int, grid, direction: str) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size)
+    rows, cols = global_shape
+    left_plain, left_t = e.basis_panels(Q_left, rows, "left")
+    right_plain, right_t = e.basis_panels(Q_right, cols, "right")
+    source = e.stage_packed("stage", matrix, global_shape)
+    e.comm.barrier()
+    lr, lc = e.rows_of(rows), e.cols_of(cols)
+    first, second = (left_plain, right_plain) if direction == "forward" else (left_t, right_t)
+    e.two_sided(source, global_shape, first, second, mode=k.EPI_STORE, out=matrix[: max(1, lr), : max(1, lc)])
+    e.comm.barrier()
+    return matrix
+
+
+def gram_update(G_local: Tensor, preconditioner: Tensor, beta: float, block_size: int, grid, shard_dim: int, side: str) -> Tensor:
+    e = engine_for(G_local.device, grid, block_size)
+    shape = torch.tensor(list(G_local.shape), dtype=torch.int64)
+    shapes = [torch.empty_like(shape) for _ in range(e.world)]
+    dist.all_gather(shapes, shape, group=e.comm.control)
+    dims = [tuple(int(v) for v in s.tolist()) for s in shapes]
+    replicated = 1 - shard_dim
+    if any(d[replicated] != dims[0][replicated] for d in dims):
+        raise ValueError(f"non-sharded dimension {replicated} must match on every rank.")
+    if any(d[shard_dim] != dims[0][shard_dim] for d in dims):
+        # unequal shards: bring them to equal contiguous shards on the host path of the control plane
+        return _gram_update_unequal(e, G_local, preconditioner, beta, shard_dim, side, dims)
+    global_shape = list(dims[0])
+    global_shape[shard_dim] *= e.world
+    rows, cols = global_shape
+    size = rows if side == "left" else cols
+    from ..layout import validate_2d_block_cyclic_buffer
+
+    validate_2d_block_cyclic_buffer(f"{side}_preconditioner", preconditioner, (size, size), block_size, grid, e.rank)
+    source = e.stage_shard(G_local, (rows, cols), shard_dim)
+    e.comm.barrier()
+    _gram_from_source(e, source, (rows, cols), preconditioner, beta, side)
+    e.comm.barrier()
+    return preconditioner
+
+
+def _gram_from_source(e: GridEngine, source: Source, shape, preconditioner: Tensor, beta: float, side: str,
+                      gathered: Optional[k.Planes] = None) -> None:
+    rows, cols = shape
+    if side == "left":    # L = G G^T: contraction over columns, operands are rows of G
+        size, depth, transpose = rows, cols, True
+    else:                 # R = G^T G: contraction over rows, operands are columns of G
+        size, depth, transpose = cols, rows, False
+    lr, lc = e.rows_of(size), e.cols_of(size)
+    a = gathered
+    if a is None:
+        a = e.planes("gram_a", depth, lr)
+        dist_gather(source, IDENTITY, e.row_map(), depth, lr, transpose=transpose, planes=a)
+    b = e.planes("gram_b", depth, lc)
+    dist_gather(source, IDENTITY, e.col_map(), depth, lc, transpose=transpose, planes=b)
+    k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta)
+
+
+def _gram_update_unequal(e: GridEngine, G_local, preconditioner, beta, shard_dim, side, dims) -> Tensor:
+    """Unequal ``tensor_split`` shards: pad every shard to the longest one with zero rows/columns
+    (zeros add nothing to a Gram matrix) and run the equal-shard path on the padded matrix."""
+    longest = max(d[shard_dim] for d in dims)
+    padded_shape = list(G_local.shape)
+    padded_shape[shard_dim] = longest
+    padded = torch.zeros(padded_shape, dtype=torch.float32, device=G_local.device)
+    padded.narrow(shard_dim, 0, G_local.shape[shard_dim]).copy_(G_local)
+    rows, cols = padded_shape
+    global_shape = [rows, cols]
+    global_shape[shard_dim] = longest * e.world
+    true_size = sum(d[shard_dim] for d in dims) if (side == "left") == (shard_dim == 0) else dims[0][1 - shard_dim]
+    source = e.stage_shard(padded, tuple(global_shape), shard_dim)
+    e.comm.barrier()
+    if (side == "left") == (shard_dim == 0):
+        # the Gram matrix is indexed by the padded dimension: map true indices to padded positions
+        position = torch.cat([torch.arange(d[shard_dim]) + r * longest for r, d in enumerate(dims)]).to(e.device)
+        size = true_size
+        depth = global_shape[1 - shard_dim]
+        transpose = side == "left"
+        lr, lc = e.rows_of(size), e.cols_of(size)
+        a, b = e.planes("gram_a", depth, lr), e.planes("gram_b", depth, lc)
+        dist_gather(source, IDENTITY, e.row_map(position), depth, lr, transpose=transpose, planes=a)
+        dist_gather(source, IDENTITY, e.col_map(position), depth, lc, transpose=transpose, planes=b)
+        k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta)
+    else:
+        _gram_from_source(e, source, tuple(global_shape), preconditioner, beta, side)
+    e.comm.barrier()
+    return preconditioner
+
+
+def _product_with_basis(e: GridEngine, P: Tensor, Q: Tensor, work: Tensor, size: int) -> None:
+    """``work <- P Q`` for symmetric packed ``P`` (so ``P^T Q``)."""
+    p_source = e.stage_packed("stage", P, (size, size))
+    q_source = e.stage_packed("basis", Q, (size, size))
+    e.comm.barrier()
+    lr, lc = e.rows_of(size), e.cols_of(size)
+    a, b = e.planes("panel_a", size, lr), e.planes("panel_b", size, lc)
+    dist_gather(p_source, IDENTITY, e.row_map(), size, lr, planes=a)
+    dist_gather(q_source, IDENTITY, e.col_map(), size, lc, planes=b)
+    k.gemm(a, b, out=work[: max(1, lr), : max(1, lc)])
+    e.comm.barrier()
+
+
+def estimated_order(P: Tensor, Q: Tensor, work: Tensor, size: int, block_size: int, grid) -> Tensor:
+    e = engine_for(P.device, grid, block_size)
+    _product_with_basis(e, P, Q, work, size)
+    lr, lc = e.rows_of(size), e.cols_of(size)
+    # partial column dots over my rows, one row of a (Pr x size) block-cyclic matrix with row blocks of 1
+    most_cols = numroc(size, e.nb, 0, e.Pc)
+    segment = e.comm.segment(f"estimates:{size}:{e.nb}", max(1, most_cols))
+    partial = segment.local[: max(1, lc)]
+    partial.zero_()
+    if lr and lc:
+        k.column_dot(Q, work, lr, lc, out=partial)
+    e.comm.barrier()
+    source = Source(segment, KIND_BLOCK_CYCLIC, e.Pr, size, 1, e.nb, e.Pr, e.Pc, e.world)
+    table = torch.empty((size, e.Pr), dtype=torch.float32, device=P.device).T   # Pr x size, column-major
+    dist_gather(source, IDENTITY, IDENTITY, e.Pr, size, out=table)
+    e.comm.barrier()
+    estimates = table.sum(dim=0)   # fixed order over Pr -> identical on every rank
+    return torch.argsort(estimates, descending=True, stable=True)
+
+
+def _gather_dense(e: GridEngine, source: Source, size: int, column_order: Optional[Tensor] = None) -> Tensor:
+    dense = torch.empty((size, size), dtype=torch.float32, device=e.device).T
+    dist_gather(source, IDENTITY, IndexMap(perm=column_order), size, size, out=dense)
+    return dense
+
+
+def _scatter_owned(e: GridEngine, dense: Tensor, packed: Tensor, size: int) -> None:
+    lr, lc = e.rows_of(size), e.cols_of(size)
+    if lr and lc:
+        rows = owned_indices(size, e.nb, e.pr, e.Pr, e.device)
+        cols = owned_indices(size, e.nb, e.pc, e.Pc, e.device)
+        k.gather2d(dense, packed[:lr, :lc], rows, cols)
+        k.mark_written(packed)
+
+
+def qr(matrix: Tensor, Q: Tensor, size: int, block_size: int, grid, column_order: Optional[Tensor] = None) -> Tensor:
+    """Householder QR of the packed ``matrix`` (columns optionally permuted on the way in).
+
+    Every rank pulls the whole (permuted) matrix, factors it with the single-GPU blocked Householder
+    kernels and keeps the tiles it owns; the factorisation is deterministic, so all ranks agree.
+    """
+    e = engine_for(matrix.device, grid, block_size)
+    source = e.stage_packed("stage", matrix, (size, size))
+    e.comm.barrier()
+    dense = _gather_dense(e, source, size, column_order)
+    e.comm.barrier()
+    full_q = torch.empty((size, size), dtype=torch.float32, device=matrix.device).T
+    factor.householder_qr(dense, full_q)
+    _scatter_owned(e, full_q, Q, size)
+    return Q
+
+
+def power_iteration_qr(P: Tensor, Q: Tensor, work: Tensor, size: int, block_size: int, grid) -> Tensor:
+    order = estimated_order(P, Q, work, size, block_size, grid)
+    qr(work, Q, size, block_size, grid, column_order=order)
+    return order
+
+
+def initialize_basis(P: Tensor, Q: Tensor, work: Tensor, eigenvalues: Tensor, size: int, block_size: int, grid,
+                     implementation: str) -> Tensor:
+    e = engine_for(P.device, grid, block_size)
+    source = e.stage_packed("stage", P, (size, size))
+    e.comm.barrier()
+    dense = _gather_dense(e, source, size)
+    e.comm.barrier()
+    full_q = torch.empty((size, size), dtype=torch.float32, device=P.device).T
+    scratch = torch.empty((size, size), dtype=torch.float32, device=P.device).T
+    factor.symmetric_eigenbasis(dense, full_q, scratch, eigenvalues, implementation)
+    _scatter_owned(e, full_q, Q, size)
+    return Q
+
+
+def permute(matrix: Tensor, global_shape, row_order: Tensor, column_order: Tensor, block_size: int, grid) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size)
+    rows, cols = global_shape
+    source = e.stage_packed("stage", matrix, global_shape)
+    e.comm.barrier()
+    lr, lc = e.rows_of(rows), e.cols_of(cols)
+    dist_gather(source, e.row_map(row_order), e.col_map(column_order), lr, lc, out=matrix[: max(1, lr), : max(1, lc)])
+    e.comm.barrier()
+    return matrix
+
+
+# ---------------------------------------------------------------------------------------------
+# The fused step
+# ---------------------------------------------------------------------------------------------
+def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global_shape, shard_dim: int, block_size: int,
+              grid, beta: float, beta1: float, beta2: float, eps: float, interval: int, implementation: str,
+              initializing: bool) -> Tensor:
+    e = engine_for(gradient_shard.device, grid, block_size)
+    rows, cols = global_shape
+    device = gradient_shard.device
+    shard_source = e.stage_shard(gradient_shard, global_shape, shard_dim)
+    e.comm.barrier()
+
+    if initializing:
+        _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
+        _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right")
+        e.comm.barrier()
+        for side, size in (("left", rows), ("right", cols)):
+            values = torch.empty(size, dtype=torch.float32, device=device)
+            initialize_basis(state[f"{side}_preconditioner"], state[f"{side}_basis"], state[f"{side}_work"], values,
+                             size, block_size, grid, implementation)
+        state["step"] = 0
+        return torch.zeros(gradient_shard.shape, dtype=torch.float32, device=device)
+
+    step = int(state["step"]) + 1
+    left_plain, left_t = e.basis_panels(state["left_basis"], rows, "left")
+    right_plain, right_t = e.basis_panels(state["right_basis"], cols, "right")
+    lr, lc = e.rows_of(rows), e.cols_of(cols)
+    bias2 = 1.0 - beta2**step
+    adam = dict(beta1=beta1, beta2=beta2, eps=eps / math.sqrt(bias2),
+                bias_correction1=1.0 - beta1**step, bias_correction2=bias2)
+    # forward rotation straight from the tensor-parallel shards, Adam in the epilogue, update -> segment
+    _, u_view, u_source = e.packed_segment("update", global_shape)
+    x_panel = e.planes("x_panel", rows, e.rows_of(cols))   # X[:, my row class]; reused by the right Gram
+    dist_gather(shard_source, IDENTITY, e.row_map(), rows, e.rows_of(cols), planes=x_panel)
+    e.two_sided(shard_source, global_shape, left_plain, right_plain, gathered=x_panel, mode=k.EPI_ADAM,
+                          out=u_view[: max(1, lr), : max(1, lc)],
+                          momentum=state["momentum"][: max(1, lr), : max(1, lc)],
+                          variance=state["variance"][: max(1, lr), : max(1, lc)], adam=adam)
+    e.comm.barrier()
+    # backward rotation, result -> segment, then every rank pulls its tensor-parallel shard
+    _, o_view, o_source = e.packed_segment("output", global_shape)
+    e.two_sided(u_source, global_shape, left_t, right_t, mode=k.EPI_STORE, out=o_view[: max(1, lr), : max(1, lc)])
+    e.comm.barrier()
+    update = _pull_shard(e, o_source, global_shape, shard_dim)
+    # Gram EMAs with the current gradient; the right Gram reuses the gathered panel X[:, my row class]
+    _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
+    _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right", gathered=x_panel)
+    e.comm.barrier()
+    if step % interval == 0:
+        refresh(e, state, global_shape)
+    state["step"] = step
+    return update
+
+
+def refresh(e: GridEngine, state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tensor]:
+    rows, cols = global_shape
+    grid, nb = e.grid, e.nb
+    rotate(state["momentum"], state["left_basis"], state["right_basis"], global_shape, nb, grid, "backward")
+    left_order = power_iteration_qr(state["left_preconditioner"], state["left_basis"], state["left_work"], rows, nb, grid)
+    right_order = power_iteration_qr(state["right_preconditioner"], state["right_basis"], state["right_work"], cols, nb, grid)
+    permute(state["variance"], global_shape, left_order, right_order, nb, grid)
+    rotate(state["momentum"], state["left_basis"], state["right_basis"], global_shape, nb, grid, "forward")
+    return left_order, right_order

@@ -15,8 +15,10 @@ from . import kernels as k
 
 def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = None) -> Tensor:
     """``Q <- explicit orthogonal factor of matrix[:, column_order]``; ``matrix`` is scratch."""
+    from ..ops.basis import count_qr_call
     from . import qr
 
+    count_qr_call()
     return qr.householder_qr(matrix, Q, column_order)
 
 

@@ -173,7 +173,7 @@ def gemm(
     mom = var = ldm = ldv = 0
     b1 = b2 = eps = ibc1 = isbc2 = 0.0
     if mode == EPI_ADAM:
-        assert momentum is not None and variance is not None and adam is not None and out_planes is not None
+        assert momentum is not None and variance is not None and adam is not None
         mom, var = momentum.data_ptr(), variance.data_ptr()
         ldm = momentum.stride(1) if momentum.shape[1] > 1 else max(1, momentum.shape[0])
         ldv = variance.stride(1) if variance.shape[1] > 1 else max(1, variance.shape[0])

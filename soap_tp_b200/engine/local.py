@@ -40,6 +40,8 @@ class BasisPlanes:
         if key == self.key:
             return
         view = Q[:size, :size]
+        if self.plain is not None and (self.plain.depth != size or self.plain.hi.device != Q.device):
+            self.plain = self.transposed = None   # the address was recycled by a tensor of another size
         self.plain = k.split_planes(view, out=self.plain)
         self.transposed = k.split_planes(view, transpose=True, out=self.transposed)
         self.key = (Q.data_ptr(), Q._version, size)
@@ -53,12 +55,13 @@ class ParameterContext:
         self.right = BasisPlanes()
 
 
-_CONTEXTS: "OrderedDict[int, ParameterContext]" = OrderedDict()
+_CONTEXTS: "OrderedDict[tuple, ParameterContext]" = OrderedDict()
 _WORKSPACES: Dict[tuple, Any] = {}
 
 
 def context_for(state: MutableMapping[str, Any]) -> ParameterContext:
-    key = state["left_basis"].data_ptr()
+    key = (state["left_basis"].data_ptr(), state["right_basis"].data_ptr(),
+           tuple(state["momentum"].shape))
     ctx = _CONTEXTS.get(key)
     if ctx is None:
         ctx = ParameterContext()

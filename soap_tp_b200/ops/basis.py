@@ -41,6 +41,12 @@ def qr_call_count() -> int:
     return _QR_CALLS
 
 
+def count_qr_call() -> None:
+    """Called by every QR factorisation, host path or device engine."""
+    global _QR_CALLS
+    _QR_CALLS += 1
+
+
 def _stable_descending_order(values: Tensor) -> Tensor:
     return torch.argsort(values, descending=True, stable=True)
 
@@ -98,7 +104,6 @@ def qr_2d_block_cyclic_(
     ``matrix`` is scratch afterwards.  Column signs are those of an unnormalised Householder
     factorisation (``R`` may have negative diagonal entries).
     """
-    global _QR_CALLS
     rank, _ = validate_world(process_grid_shape)
     for name, buffer in (("matrix", matrix), ("Q", Q)):
         validate_float_buffer(name, buffer, (size, size), block_size, process_grid_shape, rank)
@@ -106,11 +111,11 @@ def qr_2d_block_cyclic_(
         raise ValueError("matrix and Q must share a device.")
     if matrix.data_ptr() == Q.data_ptr():
         raise ValueError("matrix and Q must not overlap.")
-    _QR_CALLS += 1
     if matrix.is_cuda:
         from ..engine import api as engine
 
         return engine.qr(matrix, Q, size, block_size, process_grid_shape)
+    count_qr_call()
     grid = process_grid_shape
     M = host.gather_block_cyclic(matrix, (size, size), block_size, grid)
     Qf, _ = torch.linalg.qr(M)
@@ -137,8 +142,6 @@ def power_iteration_qr_2d_block_cyclic_(
             validate_float_buffer(name, matrix, (size, size), block_size, process_grid_shape, rank)
         if len({preconditioner.data_ptr(), Q.data_ptr(), work.data_ptr()}) != 3:
             raise ValueError("preconditioner, Q, and work must not overlap.")
-        global _QR_CALLS
-        _QR_CALLS += 1
         from ..engine import api as engine
 
         return engine.power_iteration_qr(preconditioner, Q, work, size, block_size, process_grid_shape)

@@ -106,9 +106,9 @@ def test_split_epilogue_chain_and_adam():
     k.gemm(t_planes, rp, mode=k.EPI_ADAM, out_planes=y_planes, out=proj, momentum=mt, variance=vt, adam=adam)
     k.check_status()
     y = expected_t.T @ r.double()                                # (Q^T X) R : 256 x 192
-    assert _rel(proj.cpu(), y) < 2e-6
     em = 0.9 * m0.T.cpu().double() + 0.1 * y
     ev = 0.99 * v0.T.cpu().double() + 0.01 * y * y
     eu = (em / adam["bias_correction1"]) / (ev.sqrt() / adam["bias_correction2"] ** 0.5 + 1e-6)
     assert _rel(mt.cpu(), em) < 2e-6 and _rel(vt.cpu(), ev) < 6e-6
     assert _rel(y_planes.dense().cpu(), eu) < 1e-5
+    assert _rel(proj.cpu(), eu) < 1e-5          # plain copy of the update

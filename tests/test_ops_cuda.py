@@ -13,7 +13,7 @@ from distributed_helpers import run_distributed
 pytestmark = pytest.mark.gpu
 
 RECT = [(8, 8), (8, 12), (12, 8), (9, 13), (13, 9)]
-TINY = (10, 2, (0.8, 0.9), 0.75, 1e-6, 1e-5)
+TINY = (10, 2, (0.8, 0.9), 0.75, 1e-6, 1e-5, "eigh", 2.0, 1e-6)   # ..., noise-floor perturbation
 
 
 def test_single_gpu_ops():
@@ -38,3 +38,38 @@ def test_single_gpu_trajectory():
     specs = [("case_soap_trajectory", (shape, 2, g, sd) + TINY)
              for shape in [(8, 8), (20, 20), (12, 12), (8, 12)] for sd in (0, 1)]
     run_distributed(cases.case_batch, 1, "cuda", specs)
+
+
+GRID4 = (2, 2)
+
+
+def test_four_ranks_ops():
+    specs = [("case_redistribute", (shape, 2, GRID4, sd)) for shape, sd in
+             [((8, 8), 0), ((20, 20), 1), ((12, 16), 0), ((9, 12), 1)]]
+    specs += [("case_redistribute", ((20, 20), 3, GRID4, 1)), ("case_redistribute", ((8, 8), 16, GRID4, 0)),
+              ("case_redistribute", ((300, 200), 64, GRID4, 1))]
+    specs += [("case_gram", (shape, 2, GRID4, sd, 0.0)) for shape in RECT for sd in (0, 1)]
+    specs += [("case_gram", ((9, 13), 2, GRID4, 1, 0.25)), ("case_gram", ((300, 520), 64, GRID4, 1, 0.25))]
+    specs += [("case_rotate", (shape, 2, GRID4)) for shape in RECT] + [("case_rotate", ((260, 390), 64, GRID4))]
+    specs += [("case_permute", ((9, 13), 2, GRID4)), ("case_permute", ((200, 300), 64, GRID4))]
+    specs += [("case_power_iteration_qr", (n, 2, GRID4)) for n in (8, 9, 13)]
+    specs += [("case_power_iteration_qr", (200, 64, GRID4)), ("case_estimated_order_and_qr", (12, 2, GRID4))]
+    specs += [("case_initialize_basis", ((8, 12), "right", 2, GRID4, "eigh")),
+              ("case_initialize_basis", ((9, 13), "left", 2, GRID4, "jacobi"))]
+    specs += [("case_refresh", (shape, 2, GRID4)) for shape in [(8, 12), (13, 9)]]
+    run_distributed(cases.case_batch, 4, "cuda", specs)
+
+
+def test_four_ranks_trajectory():
+    specs = [("case_soap_trajectory", (shape, 2, GRID4, sd) + TINY)
+             for shape in [(8, 8), (20, 20), (12, 12)] for sd in (0, 1)]
+    specs += [("case_soap_trajectory", ((8, 12), 2, GRID4, 1) + TINY)]
+    run_distributed(cases.case_batch, 4, "cuda", specs)
+
+
+def test_two_ranks_and_eight_ranks():
+    run_distributed(cases.case_batch, 2, "cuda", [
+        ("case_rotate", ((9, 13), 2, (1, 2))), ("case_gram", ((9, 13), 2, (2, 1), 0, 0.5)),
+        ("case_soap_trajectory", ((12, 12), 2, (1, 2), 1) + TINY)])
+    run_distributed(cases.case_batch, 8, "cuda", [
+        ("case_rotate", ((40, 24), 4, (2, 4))), ("case_soap_trajectory", ((16, 16), 2, (2, 4), 1) + TINY)])
