@@ -12,6 +12,7 @@
 #include "comm.h"
 #include "elementwise.h"
 #include "gemm.h"
+#include "qr.h"
 
 namespace py = pybind11;
 using namespace soapb200;
@@ -34,7 +35,8 @@ PYBIND11_MODULE(_C, m) {
       [](uint64_t a_hi, uint64_t a_lo, int64_t lda, uint64_t b_hi, uint64_t b_lo, int64_t ldb, int M, int N, int K,
          int mode, int symmetric, int force_narrow, float alpha, float beta, uint64_t C, int64_t ldc, uint64_t Chi,
          uint64_t Clo, int64_t ldp, uint64_t mom, uint64_t var, int64_t ldm, int64_t ldv, float beta1, float beta2,
-         float eps, float inv_bc1, float inv_sqrt_bc2, uint64_t status, uint64_t stream) {
+         float eps, float inv_bc1, float inv_sqrt_bc2, int k_splits, int64_t split_stride, uint64_t status,
+         uint64_t stream) {
         GemmOperands ops{ptr<const float>(a_hi), ptr<const float>(a_lo), lda,
                          ptr<const float>(b_hi), ptr<const float>(b_lo), ldb};
         GemmProblem prob{};
@@ -46,6 +48,7 @@ PYBIND11_MODULE(_C, m) {
         prob.mom = ptr<float>(mom); prob.var = ptr<float>(var); prob.ldm = ldm; prob.ldv = ldv;
         prob.beta1 = beta1; prob.beta2 = beta2; prob.eps = eps;
         prob.inv_bc1 = inv_bc1; prob.inv_sqrt_bc2 = inv_sqrt_bc2;
+        prob.k_splits = k_splits; prob.split_stride = split_stride;
         py::gil_scoped_release release;
         gemm_tf32x3(ops, prob, ptr<int>(status), stream_of(stream));
       },
@@ -84,6 +87,31 @@ PYBIND11_MODULE(_C, m) {
           gather2d(ptr<const float>(src), s_i, s_j, ptr<float>(dst), d_i, d_j, ptr<const int64_t>(row_map),
                    ptr<const int64_t>(col_map), rows, cols, stream_of(stream));
         });
+
+  m.def("qr_panel",
+        [](uint64_t p_hi, uint64_t p_lo, int64_t ldp, int r, int b, uint64_t v_hi, uint64_t v_lo, int64_t ldv,
+           uint64_t vt_hi, uint64_t vt_lo, int64_t ldvt, uint64_t tau, uint64_t S, uint64_t exchange, uint64_t stream) {
+          qr_panel(ptr<const float>(p_hi), ptr<const float>(p_lo), ldp, r, b, ptr<float>(v_hi), ptr<float>(v_lo), ldv,
+                   ptr<float>(vt_hi), ptr<float>(vt_lo), ldvt, ptr<float>(tau), ptr<float>(S), ptr<float>(exchange),
+                   stream_of(stream));
+        });
+  m.def("qr_larft",
+        [](uint64_t S, uint64_t tau, int b, uint64_t t_hi, uint64_t t_lo, uint64_t tt_hi, uint64_t tt_lo, int64_t ldt,
+           uint64_t stream) {
+          qr_larft(ptr<const float>(S), ptr<const float>(tau), b, ptr<float>(t_hi), ptr<float>(t_lo), ptr<float>(tt_hi),
+                   ptr<float>(tt_lo), ldt, stream_of(stream));
+        });
+  m.def("sum_partials_to_planes",
+        [](uint64_t partials, int splits, int64_t stride, int64_t ld, uint64_t hi, uint64_t lo, int64_t ldp, int rows,
+           int cols, uint64_t stream) {
+          sum_partials_to_planes(ptr<const float>(partials), splits, stride, ld, ptr<float>(hi), ptr<float>(lo), ldp, rows,
+                                 cols, stream_of(stream));
+        });
+  m.def("identity_planes", [](uint64_t hi, uint64_t lo, int64_t ldp, int rows, int cols, uint64_t stream) {
+    identity_planes(ptr<float>(hi), ptr<float>(lo), ldp, rows, cols, stream_of(stream));
+  });
+  m.attr("QR_PANEL_WIDTH") = kQrPanelWidth;
+  m.attr("QR_ROWS_PER_CTA") = kQrRowsPerCta;
 
   register_comm(m);
 }

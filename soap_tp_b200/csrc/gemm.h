@@ -7,7 +7,7 @@ namespace soapb200 {
 
 enum EpilogueMode : int {
   kEpiStore = 0,     // C[m + n*ldc] = alpha*acc + beta*C   (EMA when beta != 0); optional symmetric mirror
-  kEpiSplit = 1,     // write alpha*acc as hi/lo planes (operand of the next GEMM); optional plain copy in C
+  kEpiSplit = 1,     // planes <- alpha*acc + beta*(old planes), as hi/lo (operand of the next GEMM); optional plain copy in C
   kEpiAdam = 2,      // acc is the projected gradient: update momentum/variance; update -> planes and/or C
   kEpiRowMajor = 3,  // C[m*ldc + n] = alpha*acc (tensor-parallel shard output)
 };
@@ -27,6 +27,8 @@ struct GemmProblem {
   int mode;
   int symmetric;     // A == B: compute tiles on/below the diagonal, mirror the rest (kEpiStore only)
   int force_narrow;  // use 128-wide tiles regardless of the problem size
+  int k_splits;      // kEpiStore: split K over this many CTAs per tile, partial s written at C + s*split_stride
+  int64_t split_stride;
   float alpha, beta;
   float* C;
   int64_t ldc;

@@ -66,16 +66,17 @@ __device__ __forceinline__ float tf32_round(float x) {
 }
 
 template <int MODE>
-__device__ __forceinline__ void epilogue_element(const GemmProblem& prob, int m, int n, float acc) {
+__device__ __forceinline__ void epilogue_element(const GemmProblem& prob, int64_t c_shift, int m, int n, float acc) {
   if constexpr (MODE == kEpiStore) {
-    float* dst = prob.C + m + static_cast<int64_t>(n) * prob.ldc;
+    float* dst = prob.C + c_shift + m + static_cast<int64_t>(n) * prob.ldc;
     float v = prob.alpha * acc;
     if (prob.beta != 0.0f) v = fmaf(prob.beta, *dst, v);
     *dst = v;
-    if (prob.symmetric && n < m) prob.C[n + static_cast<int64_t>(m) * prob.ldc] = v;
+    if (prob.symmetric && n < m) prob.C[c_shift + n + static_cast<int64_t>(m) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiSplit) {
     const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
-    const float v = prob.alpha * acc;
+    float v = prob.alpha * acc;
+    if (prob.beta != 0.0f) v = fmaf(prob.beta, prob.Chi[off] + prob.Clo[off], v);  // planes hold the old value
     const float hi = tf32_round(v);
     prob.Chi[off] = hi;
     prob.Clo[off] = v - hi;
@@ -161,7 +162,12 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int k_blocks = (prob.K + kBK - 1) / kBK;
+  // Split-K (kEpiStore only): blockIdx.y owns k-blocks [kb_first, kb_first + k_blocks) and writes its
+  // own partial result at C + blockIdx.y * split_stride; the caller sums the partials in fixed order.
+  const int total_k_blocks = (prob.K + kBK - 1) / kBK;
+  const int per_split = (total_k_blocks + gridDim.y - 1) / gridDim.y;
+  const int kb_first = blockIdx.y * per_split;
+  const int k_blocks = max(0, min(total_k_blocks, kb_first + per_split) - kb_first);
   const int chunks = (k_blocks + kPromote - 1) / kPromote;
 
   if (warp == 0 && lane == 0) {
@@ -174,7 +180,7 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
         break;
       uint8_t* stage = smem + s * Cfg::kStageBytes;
       mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
-      const int k0 = kb * kBK;
+      const int k0 = (kb_first + kb) * kBK;
       tma_load_2d(stage, &maps.a_hi, &full_bar[s], k0, m0);
       tma_load_2d(stage + kBM * 128, &maps.a_lo, &full_bar[s], k0, m0);
       tma_load_2d(stage + 2 * kBM * 128, &maps.b_hi, &full_bar[s], k0, n0);
@@ -254,10 +260,11 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     if (ok && m < prob.M) {
+      const int64_t c_shift = (gridDim.y > 1) ? static_cast<int64_t>(blockIdx.y) * prob.split_stride : 0;
 #pragma unroll
       for (int j = 0; j < kCols; ++j) {
         const int n = n0 + col0 + j;
-        if (n < prob.N && !(prob.symmetric && n > m)) epilogue_element<MODE>(prob, m, n, sum[j]);
+        if (n < prob.N && !(prob.symmetric && n > m)) epilogue_element<MODE>(prob, c_shift, m, n, sum[j]);
       }
     }
   }
@@ -323,7 +330,9 @@ void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaS
   maps.b_lo = make_operand_map(ops.b_lo, prob.K, prob.N, ops.ldb, BN);
   const int tiles_m = (prob.M + kBM - 1) / kBM;
   const int tiles_n = (prob.N + BN - 1) / BN;
-  gemm_tf32x3_kernel<BN, MODE><<<tiles_m * tiles_n, kThreads, Cfg::kSmemBytes, stream>>>(maps, prob, status);
+  const int splits = (MODE == kEpiStore && prob.k_splits > 1) ? prob.k_splits : 1;
+  dim3 grid(tiles_m * tiles_n, splits);
+  gemm_tf32x3_kernel<BN, MODE><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(maps, prob, status);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) throw std::runtime_error(std::string("gemm_tf32x3 launch: ") + cudaGetErrorString(err));
 }

@@ -103,6 +103,11 @@ class Planes:
         storage = torch.empty((2, max(1, cols), ld), dtype=torch.float32, device=device)
         return Planes(storage[0], storage[1], depth, cols, ld)
 
+    def sub(self, k0: int, c0: int, depth: int, cols: int) -> "Planes":
+        """Operand planes of the sub-matrix starting at row ``k0`` (a multiple of 4), column ``c0``."""
+        assert k0 % 4 == 0 and k0 + depth <= self.ld and c0 + cols <= self.hi.shape[0]
+        return Planes(self.hi[c0:, k0:], self.lo[c0:, k0:], depth, cols, self.ld)
+
     def dense(self) -> Tensor:
         """The represented K x cols matrix (for tests)."""
         return (self.hi[: self.cols, : self.depth] + self.lo[: self.cols, : self.depth]).T
@@ -147,6 +152,8 @@ def gemm(
     variance: Optional[Tensor] = None,
     adam: Optional[dict] = None,
     force_narrow: bool = False,
+    k_splits: int = 1,
+    split_stride: int = 0,
 ) -> None:
     """``acc[m, n] = sum_k a[k, m] * b[k, n]`` then the fused epilogue (see ``csrc/gemm.h``).
 
@@ -182,7 +189,8 @@ def gemm(
     status = status_word(a.hi.device)
     _C.gemm_tf32x3(a.hi.data_ptr(), a.lo.data_ptr(), a.ld, b.hi.data_ptr(), b.lo.data_ptr(), b.ld, M, N, K,
                    mode, int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
-                   mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, status.data_ptr(), _stream())
+                   mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, int(k_splits), int(split_stride), status.data_ptr(),
+                   _stream())
     mark_written(out, momentum, variance)
     _count("gemm_tf32x3_kernel")
 

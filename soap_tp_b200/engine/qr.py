@@ -1,14 +1,129 @@
-"""Householder QR of a local column-major matrix (bring-up version: library factorisation)."""
+"""Blocked Householder QR on one GPU with tensor-core trailing updates.
+
+``householder_qr(A, Q, order)`` overwrites ``Q`` with the explicit orthogonal factor of
+``A[:, order]``, the contract of the reference's ``slate_qr_float`` (``geqrf`` + ``unmqr`` on an
+identity, ``src/soap_tp/csrc/slate_bindings.cpp:125-189``).  Per 128-column panel:
+
+    panel kernel (cooperative, panel resident in shared memory)  -> V, V^T planes, tau, V^T V
+    larft kernel                                                  -> T, T^T planes
+    Z = T V^T                      (3xTF32 tcgen05 GEMM, K = 128)
+    W = V^T C_trailing             (split-K GEMM, partials summed in fixed order -> deterministic)
+    C_trailing -= Z^T W            (GEMM whose epilogue read-modify-writes the operand planes)
+
+and the same three GEMMs in reverse panel order build the explicit ``Q`` from the identity.  The
+trailing matrix and ``Q`` live as hi/lo operand planes throughout, so no separate split pass is
+needed between panels.  All arithmetic is fp32-class (3xTF32 products, fp32 panel).
+"""
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 from torch import Tensor
 
+from . import kernels as k
+
+_C = k._C
+PANEL = _C.QR_PANEL_WIDTH
+_WORKSPACES: Dict[tuple, dict] = {}
+
+
+def _workspace(n: int, device) -> dict:
+    key = (n, str(device))
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        panels = -(-n // PANEL)
+        ws = {
+            "C": k.Planes.empty(n, n, device),
+            "Q": k.Planes.empty(n, n, device),
+            "V": k.Planes.empty(n, n, device),
+            "Vt": [k.Planes.empty(min(PANEL, n - p * PANEL), n, device) for p in range(panels)],
+            "T": [k.Planes.empty(min(PANEL, n - p * PANEL), PANEL, device) for p in range(panels)],
+            "Tt": [k.Planes.empty(min(PANEL, n - p * PANEL), PANEL, device) for p in range(panels)],
+            "Z": k.Planes.empty(PANEL, n, device),
+            "W": k.Planes.empty(PANEL, n, device),
+            "tau": torch.zeros(n + PANEL, dtype=torch.float32, device=device),
+            "S": torch.zeros(PANEL * PANEL, dtype=torch.float32, device=device),
+            "exchange": torch.zeros(4 * 160 * PANEL + 4 * PANEL, dtype=torch.float32, device=device),
+            "partials": torch.empty(16 * PANEL * n, dtype=torch.float32, device=device),
+            "staging": torch.empty((n, n), dtype=torch.float32, device=device).T,
+        }
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    _WORKSPACES.clear()
+
+
+def _splits(tiles: int, k_blocks: int) -> int:
+    wanted = max(1, -(-296 // max(1, tiles)))
+    return max(1, min(wanted, 16, max(1, k_blocks // 4)))
+
+
+def _skinny_product(ws: dict, a: k.Planes, b: k.Planes, out: k.Planes) -> None:
+    """``out <- a^T b`` for a narrow ``a`` (at most 128 columns): split-K partials + ordered sum."""
+    M, N, K = a.cols, b.cols, a.depth
+    splits = _splits(-(-N // 128), -(-K // 32))
+    ld = M
+    partials = ws["partials"]
+    view = partials[: ld * N].view(N, ld).T
+    k.gemm(a, b, mode=k.EPI_STORE, out=view, out_ld=ld, force_narrow=True, k_splits=splits, split_stride=ld * N)
+    _C.sum_partials_to_planes(partials.data_ptr(), splits, ld * N, ld, out.hi.data_ptr(), out.lo.data_ptr(), out.ld,
+                              M, N, k._stream())
+    k._count("sum_partials_kernel")
+
 
 def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = None) -> Tensor:
-    source = matrix if column_order is None else matrix[:, column_order]
-    factor, _ = torch.linalg.qr(source)
-    Q.copy_(factor)
+    n = matrix.shape[0]
+    assert matrix.shape == (n, n) and Q.shape == (n, n)
+    device = matrix.device
+    ws = _workspace(n, device)
+    C, Qp, V = ws["C"], ws["Q"], ws["V"]
+    source = matrix
+    if column_order is not None:
+        source = ws["staging"]
+        k.gather2d(matrix, source, None, column_order)
+    k.split_planes(source, out=C)
+    stream = k._stream
+    panels = list(range(0, n, PANEL))
+    for p, j0 in enumerate(panels):
+        bw, r = min(PANEL, n - j0), n - j0
+        nc = n - j0 - bw
+        panel, v, vt = C.sub(j0, j0, r, bw), V.sub(j0, j0, r, bw), ws["Vt"][p]
+        tau = ws["tau"][j0:]
+        _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(), v.ld,
+                    vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), ws["S"].data_ptr(),
+                    ws["exchange"].data_ptr(), stream())
+        k._count("qr_panel_kernel")
+        T, Tt = ws["T"][p], ws["Tt"][p]
+        _C.qr_larft(ws["S"].data_ptr(), tau.data_ptr(), bw, T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(),
+                    Tt.lo.data_ptr(), T.ld, stream())
+        k._count("larft_kernel")
+        if nc > 0:
+            t_op = k.Planes(Tt.hi, Tt.lo, bw, bw, Tt.ld)
+            vt_op = vt.sub(0, 0, bw, r)
+            z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else k.Planes.empty(bw, r, device)
+            k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z, force_narrow=True)            # Z = T V^T
+            w = ws["W"].sub(0, 0, bw, nc) if bw == PANEL else k.Planes.empty(bw, nc, device)
+            trailing = C.sub(j0, j0 + bw, r, nc)
+            _skinny_product(ws, v, trailing, w)                                             # W = V^T C
+            k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=trailing, alpha=-1.0, beta=1.0)        # C -= Z^T W
+    # explicit Q = H_0 H_1 ... applied to the identity, last panel first
+    _C.identity_planes(Qp.hi.data_ptr(), Qp.lo.data_ptr(), Qp.ld, n, n, stream())
+    k._count("identity_planes_kernel")
+    for p in reversed(range(len(panels))):
+        j0 = panels[p]
+        bw, r = min(PANEL, n - j0), n - j0
+        v, vt, T = V.sub(j0, j0, r, bw), ws["Vt"][p], ws["T"][p]
+        t_op = k.Planes(T.hi, T.lo, bw, bw, T.ld)
+        vt_op = vt.sub(0, 0, bw, r)
+        z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else k.Planes.empty(bw, r, device)
+        k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z, force_narrow=True)                # Z = T^T V^T
+        block = Qp.sub(j0, j0, r, r)
+        w = ws["W"].sub(0, 0, bw, r) if bw == PANEL else k.Planes.empty(bw, r, device)
+        _skinny_product(ws, v, block, w)                                                    # W = V^T Q
+        k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0,
+               out=Q if p == 0 else None)                                                   # Q -= Z^T W
+    k.mark_written(Q)
     return Q
