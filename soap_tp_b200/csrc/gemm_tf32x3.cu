@@ -65,30 +65,49 @@ __device__ __forceinline__ float tf32_round(float x) {
   return __uint_as_float(r);
 }
 
+// The epilogue is split in two so that the read half of every read-modify-write (EMA, planes
+// accumulate, Adam moments) is issued for a whole batch of columns before any store: a load that
+// follows a store to a possibly aliasing address cannot be hoisted by the compiler, and one
+// dependent DRAM round trip per element would dominate short-K products.
 template <int MODE>
-__device__ __forceinline__ void epilogue_element(const GemmProblem& prob, int64_t c_shift, int m, int n, float acc) {
+__device__ __forceinline__ void epilogue_prefetch(const GemmProblem& prob, int64_t c_shift, int m, int n, float& old0,
+                                                  float& old1) {
   if constexpr (MODE == kEpiStore) {
-    float* dst = prob.C + c_shift + m + static_cast<int64_t>(n) * prob.ldc;
+    if (prob.beta != 0.0f) old0 = prob.C[c_shift + m + static_cast<int64_t>(n) * prob.ldc];
+  } else if constexpr (MODE == kEpiSplit) {
+    if (prob.beta != 0.0f) {
+      const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
+      old0 = prob.Chi[off];
+      old1 = prob.Clo[off];
+    }
+  } else if constexpr (MODE == kEpiAdam) {
+    old0 = prob.mom[m + static_cast<int64_t>(n) * prob.ldm];
+    old1 = prob.var[m + static_cast<int64_t>(n) * prob.ldv];
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ void epilogue_finish(const GemmProblem& prob, int64_t c_shift, int m, int n, float acc,
+                                                float old0, float old1) {
+  if constexpr (MODE == kEpiStore) {
     float v = prob.alpha * acc;
-    if (prob.beta != 0.0f) v = fmaf(prob.beta, *dst, v);
-    *dst = v;
+    if (prob.beta != 0.0f) v = fmaf(prob.beta, old0, v);
+    prob.C[c_shift + m + static_cast<int64_t>(n) * prob.ldc] = v;
     if (prob.symmetric && n < m) prob.C[c_shift + n + static_cast<int64_t>(m) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiSplit) {
     const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
     float v = prob.alpha * acc;
-    if (prob.beta != 0.0f) v = fmaf(prob.beta, prob.Chi[off] + prob.Clo[off], v);  // planes hold the old value
+    if (prob.beta != 0.0f) v = fmaf(prob.beta, old0 + old1, v);  // planes hold the old value
     const float hi = tf32_round(v);
     prob.Chi[off] = hi;
     prob.Clo[off] = v - hi;
     if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiAdam) {
-    float* mp = prob.mom + m + static_cast<int64_t>(n) * prob.ldm;
-    float* vp = prob.var + m + static_cast<int64_t>(n) * prob.ldv;
     const float g = acc;
-    const float mo = fmaf(prob.beta1, *mp, (1.0f - prob.beta1) * g);
-    const float va = fmaf(prob.beta2, *vp, (1.0f - prob.beta2) * g * g);
-    *mp = mo;
-    *vp = va;
+    const float mo = fmaf(prob.beta1, old0, (1.0f - prob.beta1) * g);
+    const float va = fmaf(prob.beta2, old1, (1.0f - prob.beta2) * g * g);
+    prob.mom[m + static_cast<int64_t>(n) * prob.ldm] = mo;
+    prob.var[m + static_cast<int64_t>(n) * prob.ldv] = va;
     const float u = (mo * prob.inv_bc1) / (sqrtf(va) * prob.inv_sqrt_bc2 + prob.eps);
     if (prob.Chi) {
       const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
@@ -261,10 +280,22 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
     }
     if (ok && m < prob.M) {
       const int64_t c_shift = (gridDim.y > 1) ? static_cast<int64_t>(blockIdx.y) * prob.split_stride : 0;
+      constexpr int kBatch = 8;
 #pragma unroll
-      for (int j = 0; j < kCols; ++j) {
-        const int n = n0 + col0 + j;
-        if (n < prob.N && !(prob.symmetric && n > m)) epilogue_element<MODE>(prob, c_shift, m, n, sum[j]);
+      for (int j0 = 0; j0 < kCols; j0 += kBatch) {
+        float old0[kBatch], old1[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const int n = n0 + col0 + j0 + u;
+          old0[u] = old1[u] = 0.0f;
+          if (n < prob.N && !(prob.symmetric && n > m)) epilogue_prefetch<MODE>(prob, c_shift, m, n, old0[u], old1[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const int n = n0 + col0 + j0 + u;
+          if (n < prob.N && !(prob.symmetric && n > m))
+            epilogue_finish<MODE>(prob, c_shift, m, n, sum[j0 + u], old0[u], old1[u]);
+        }
       }
     }
   }

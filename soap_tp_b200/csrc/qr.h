@@ -13,9 +13,11 @@ constexpr int kQrMaxRows = 148 * kQrRowsPerCta;
 // b Householder reflectors H_c = I - tau_c v_c v_c^T (v_c[c] = 1, zeros above).
 // Outputs: V as planes (r x b, unit lower trapezoid, pitch ldv), V^T as planes (b x r, pitch ldvt),
 // tau[b], and S[b x b] (column-major) with S[j, c] = v_j^T v_c for j < c (input of larft).
-// `exchange` is scratch of at least 4 * gridsize * b + 4 * b floats.  Cooperative launch.
+// `exchange` is 8-byte-aligned scratch of at least 4 * (gridsize + 1) * 128 floats that persists
+// between calls; `status` is the device status word a timed-out exchange reports to.  Cooperative launch.
 void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, float* v_hi, float* v_lo, int64_t ldv,
-              float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* S, float* exchange, cudaStream_t stream);
+              float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* S, float* exchange, int* status,
+              cudaStream_t stream);
 
 // Triangular factor of the compact WY form H_0 ... H_{b-1} = I - V T V^T from S and tau; T (b x b,
 // upper triangular) is written as operand planes in both orientations (pitch ldt each).

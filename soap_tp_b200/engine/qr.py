@@ -94,7 +94,7 @@ def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = N
         tau = ws["tau"][j0:]
         _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(), v.ld,
                     vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), ws["S"].data_ptr(),
-                    ws["exchange"].data_ptr(), stream())
+                    ws["exchange"].data_ptr(), k.status_word(device).data_ptr(), stream())
         k._count("qr_panel_kernel")
         T, Tt = ws["T"][p], ws["Tt"][p]
         _C.qr_larft(ws["S"].data_ptr(), tau.data_ptr(), bw, T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(),
