@@ -90,17 +90,11 @@ PYBIND11_MODULE(_C, m) {
 
   m.def("qr_panel",
         [](uint64_t p_hi, uint64_t p_lo, int64_t ldp, int r, int b, uint64_t v_hi, uint64_t v_lo, int64_t ldv,
-           uint64_t vt_hi, uint64_t vt_lo, int64_t ldvt, uint64_t tau, uint64_t S, uint64_t exchange, uint64_t status,
-           uint64_t stream) {
+           uint64_t vt_hi, uint64_t vt_lo, int64_t ldvt, uint64_t tau, uint64_t t_hi, uint64_t t_lo, uint64_t tt_hi,
+           uint64_t tt_lo, int64_t ldt, uint64_t exchange, uint64_t status, uint64_t stream) {
           qr_panel(ptr<const float>(p_hi), ptr<const float>(p_lo), ldp, r, b, ptr<float>(v_hi), ptr<float>(v_lo), ldv,
-                   ptr<float>(vt_hi), ptr<float>(vt_lo), ldvt, ptr<float>(tau), ptr<float>(S), ptr<float>(exchange),
-                   ptr<int>(status), stream_of(stream));
-        });
-  m.def("qr_larft",
-        [](uint64_t S, uint64_t tau, int b, uint64_t t_hi, uint64_t t_lo, uint64_t tt_hi, uint64_t tt_lo, int64_t ldt,
-           uint64_t stream) {
-          qr_larft(ptr<const float>(S), ptr<const float>(tau), b, ptr<float>(t_hi), ptr<float>(t_lo), ptr<float>(tt_hi),
-                   ptr<float>(tt_lo), ldt, stream_of(stream));
+                   ptr<float>(vt_hi), ptr<float>(vt_lo), ldvt, ptr<float>(tau), ptr<float>(t_hi), ptr<float>(t_lo),
+                   ptr<float>(tt_hi), ptr<float>(tt_lo), ldt, ptr<float>(exchange), ptr<int>(status), stream_of(stream));
         });
   m.def("sum_partials_to_planes",
         [](uint64_t partials, int splits, int64_t stride, int64_t ld, uint64_t hi, uint64_t lo, int64_t ldp, int rows,
@@ -113,6 +107,7 @@ PYBIND11_MODULE(_C, m) {
   });
   m.attr("QR_PANEL_WIDTH") = kQrPanelWidth;
   m.attr("QR_ROWS_PER_CTA") = kQrRowsPerCta;
+  m.attr("QR_MAX_ROWS") = kQrMaxRows;
 
   register_comm(m);
 }

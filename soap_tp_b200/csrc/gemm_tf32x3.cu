@@ -65,49 +65,43 @@ __device__ __forceinline__ float tf32_round(float x) {
   return __uint_as_float(r);
 }
 
-// The epilogue is split in two so that the read half of every read-modify-write (EMA, planes
-// accumulate, Adam moments) is issued for a whole batch of columns before any store: a load that
-// follows a store to a possibly aliasing address cannot be hoisted by the compiler, and one
-// dependent DRAM round trip per element would dominate short-K products.
-template <int MODE>
-__device__ __forceinline__ void epilogue_prefetch(const GemmProblem& prob, int64_t c_shift, int m, int n, float& old0,
-                                                  float& old1) {
-  if constexpr (MODE == kEpiStore) {
-    if (prob.beta != 0.0f) old0 = prob.C[c_shift + m + static_cast<int64_t>(n) * prob.ldc];
-  } else if constexpr (MODE == kEpiSplit) {
-    if (prob.beta != 0.0f) {
-      const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
-      old0 = prob.Chi[off];
-      old1 = prob.Clo[off];
-    }
-  } else if constexpr (MODE == kEpiAdam) {
-    old0 = prob.mom[m + static_cast<int64_t>(n) * prob.ldm];
-    old1 = prob.var[m + static_cast<int64_t>(n) * prob.ldv];
-  }
+constexpr int kTilePitch = kBM + 4;   // floats between columns of the staged tile (keeps 16-byte alignment)
+
+struct Vec4 {
+  float v[4];
+};
+__device__ __forceinline__ Vec4 load4(const float* p) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  return Vec4{{x.x, x.y, x.z, x.w}};
+}
+__device__ __forceinline__ void store4(float* p, const Vec4& x) {
+  *reinterpret_cast<float4*>(p) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
 }
 
+// One output element (scalar path: ragged tiles, unaligned pitches, the diagonal band of symmetric products).
 template <int MODE>
-__device__ __forceinline__ void epilogue_finish(const GemmProblem& prob, int64_t c_shift, int m, int n, float acc,
-                                                float old0, float old1) {
+__device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t c_shift, int m, int n, float acc) {
   if constexpr (MODE == kEpiStore) {
+    float* dst = prob.C + c_shift + m + static_cast<int64_t>(n) * prob.ldc;
     float v = prob.alpha * acc;
-    if (prob.beta != 0.0f) v = fmaf(prob.beta, old0, v);
-    prob.C[c_shift + m + static_cast<int64_t>(n) * prob.ldc] = v;
+    if (prob.beta != 0.0f) v = fmaf(prob.beta, *dst, v);
+    *dst = v;
     if (prob.symmetric && n < m) prob.C[c_shift + n + static_cast<int64_t>(m) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiSplit) {
     const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
     float v = prob.alpha * acc;
-    if (prob.beta != 0.0f) v = fmaf(prob.beta, old0 + old1, v);  // planes hold the old value
+    if (prob.beta != 0.0f) v = fmaf(prob.beta, prob.Chi[off] + prob.Clo[off], v);  // planes hold the old value
     const float hi = tf32_round(v);
     prob.Chi[off] = hi;
     prob.Clo[off] = v - hi;
     if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiAdam) {
-    const float g = acc;
-    const float mo = fmaf(prob.beta1, old0, (1.0f - prob.beta1) * g);
-    const float va = fmaf(prob.beta2, old1, (1.0f - prob.beta2) * g * g);
-    prob.mom[m + static_cast<int64_t>(n) * prob.ldm] = mo;
-    prob.var[m + static_cast<int64_t>(n) * prob.ldv] = va;
+    float* mp = prob.mom + m + static_cast<int64_t>(n) * prob.ldm;
+    float* vp = prob.var + m + static_cast<int64_t>(n) * prob.ldv;
+    const float mo = fmaf(prob.beta1, *mp, (1.0f - prob.beta1) * acc);
+    const float va = fmaf(prob.beta2, *vp, (1.0f - prob.beta2) * acc * acc);
+    *mp = mo;
+    *vp = va;
     const float u = (mo * prob.inv_bc1) / (sqrtf(va) * prob.inv_sqrt_bc2 + prob.eps);
     if (prob.Chi) {
       const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
@@ -116,8 +110,136 @@ __device__ __forceinline__ void epilogue_finish(const GemmProblem& prob, int64_t
       prob.Clo[off] = u - hi;
     }
     if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = u;
-  } else {  // kEpiRowMajor
-    prob.C[static_cast<int64_t>(m) * prob.ldc + n] = prob.alpha * acc;
+  }
+}
+
+// Old values a column needs (the read half of the read-modify-write), four rows per lane.
+template <int MODE>
+__device__ __forceinline__ void epilogue_load4(const GemmProblem& prob, int64_t c_shift, int m, int n, Vec4& old0, Vec4& old1) {
+  if constexpr (MODE == kEpiStore) {
+    if (prob.beta != 0.0f) old0 = load4(prob.C + c_shift + m + static_cast<int64_t>(n) * prob.ldc);
+  } else if constexpr (MODE == kEpiSplit) {
+    if (prob.beta != 0.0f) {
+      old0 = load4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp);
+      old1 = load4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp);
+    }
+  } else if constexpr (MODE == kEpiAdam) {
+    old0 = load4(prob.mom + m + static_cast<int64_t>(n) * prob.ldm);
+    old1 = load4(prob.var + m + static_cast<int64_t>(n) * prob.ldv);
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t c_shift, int m, int n, const Vec4& acc,
+                                                const Vec4& old0, const Vec4& old1) {
+  if constexpr (MODE == kEpiStore) {
+    Vec4 out;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = prob.alpha * acc.v[i];
+      if (prob.beta != 0.0f) v = fmaf(prob.beta, old0.v[i], v);
+      out.v[i] = v;
+    }
+    store4(prob.C + c_shift + m + static_cast<int64_t>(n) * prob.ldc, out);
+    if (prob.symmetric) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (n < m + i) prob.C[c_shift + n + static_cast<int64_t>(m + i) * prob.ldc] = out.v[i];
+    }
+  } else if constexpr (MODE == kEpiSplit) {
+    Vec4 hi, lo, plain;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = prob.alpha * acc.v[i];
+      if (prob.beta != 0.0f) v = fmaf(prob.beta, old0.v[i] + old1.v[i], v);
+      plain.v[i] = v;
+      hi.v[i] = tf32_round(v);
+      lo.v[i] = v - hi.v[i];
+    }
+    store4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp, hi);
+    store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
+    if (prob.C) store4(prob.C + m + static_cast<int64_t>(n) * prob.ldc, plain);
+  } else if constexpr (MODE == kEpiAdam) {
+    Vec4 mo, va, u, hi, lo;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float g = acc.v[i];
+      mo.v[i] = fmaf(prob.beta1, old0.v[i], (1.0f - prob.beta1) * g);
+      va.v[i] = fmaf(prob.beta2, old1.v[i], (1.0f - prob.beta2) * g * g);
+      u.v[i] = (mo.v[i] * prob.inv_bc1) / (sqrtf(va.v[i]) * prob.inv_sqrt_bc2 + prob.eps);
+      hi.v[i] = tf32_round(u.v[i]);
+      lo.v[i] = u.v[i] - hi.v[i];
+    }
+    store4(prob.mom + m + static_cast<int64_t>(n) * prob.ldm, mo);
+    store4(prob.var + m + static_cast<int64_t>(n) * prob.ldv, va);
+    if (prob.Chi) {
+      store4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp, hi);
+      store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
+    }
+    if (prob.C) store4(prob.C + m + static_cast<int64_t>(n) * prob.ldc, u);
+  }
+}
+
+__device__ __forceinline__ bool aligned16(const void* p, int64_t pitch_floats) {
+  return p == nullptr || (((reinterpret_cast<uintptr_t>(p) & 15) == 0) && (pitch_floats & 3) == 0);
+}
+
+// Fused epilogue over the staged tile (tile[n_local * kTilePitch + m_local]).  `ew` is the index of the
+// calling warp among the kEpiWarps epilogue warps.
+template <int BN, int MODE>
+__device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const float* tile, int m0, int n0, int ew, int lane,
+                                             int64_t c_shift) {
+  const int rows = min(kBM, prob.M - m0);
+  const int cols = min(BN, prob.N - n0);
+  if constexpr (MODE == kEpiRowMajor) {
+    // one warp per output row, lanes sweep the columns so the stores are contiguous
+    for (int r = ew; r < rows; r += kEpiWarps) {
+      float* dst = prob.C + static_cast<int64_t>(m0 + r) * prob.ldc + n0;
+      for (int n = lane; n < cols; n += 32) dst[n] = prob.alpha * tile[n * kTilePitch + r];
+    }
+    return;
+  }
+  bool vector = rows == kBM;
+  if constexpr (MODE == kEpiStore) vector = vector && aligned16(prob.C + c_shift, prob.ldc);
+  if constexpr (MODE == kEpiSplit)
+    vector = vector && aligned16(prob.Chi, prob.ldp) && aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);
+  if constexpr (MODE == kEpiAdam)
+    vector = vector && aligned16(prob.mom, prob.ldm) && aligned16(prob.var, prob.ldv) && aligned16(prob.Chi, prob.ldp) &&
+             aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);
+  if (!vector) {
+    for (int nl = ew; nl < cols; nl += kEpiWarps) {
+      const int n = n0 + nl;
+      for (int r = lane; r < rows; r += 32) {
+        const int m = m0 + r;
+        if (prob.symmetric && n > m) continue;
+        epilogue_scalar<MODE>(prob, c_shift, m, n, tile[nl * kTilePitch + r]);
+      }
+    }
+    return;
+  }
+  constexpr int kUnroll = 4;   // columns per warp whose loads are in flight together
+  const int m = m0 + 4 * lane;
+  for (int base = ew * kUnroll; base < cols; base += kEpiWarps * kUnroll) {
+    Vec4 old0[kUnroll], old1[kUnroll];
+    int state[kUnroll];        // 0: skip, 1: vector, 2: element by element (diagonal band of a symmetric product)
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int nl = base + u, n = n0 + nl;
+      state[u] = (nl < cols) ? 1 : 0;
+      if (prob.symmetric && state[u]) state[u] = (n > m + 3) ? 0 : (n > m ? 2 : 1);
+      old0[u] = old1[u] = Vec4{{0.f, 0.f, 0.f, 0.f}};
+      if (state[u] == 1) epilogue_load4<MODE>(prob, c_shift, m, n, old0[u], old1[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int nl = base + u, n = n0 + nl;
+      if (state[u] == 1) {
+        epilogue_store4<MODE>(prob, c_shift, m, n, load4(tile + nl * kTilePitch + 4 * lane), old0[u], old1[u]);
+      } else if (state[u] == 2) {
+        for (int i = 0; i < 4; ++i)
+          if (n <= m + i) epilogue_scalar<MODE>(prob, c_shift, m + i, n, tile[nl * kTilePitch + 4 * lane + i]);
+      }
+    }
   }
 }
 
@@ -254,7 +376,6 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
     const int half = ew >> 2;                  // which half of the tile's columns
     constexpr int kCols = Cfg::kColsPerThread;
     const int col0 = half * kCols;
-    const int m = m0 + quarter * 32 + lane;
     float sum[kCols];
 #pragma unroll
     for (int j = 0; j < kCols; ++j) sum[j] = 0.0f;
@@ -278,25 +399,20 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
-    if (ok && m < prob.M) {
+    // Stage the running sums in shared memory (the pipeline stages are idle once the last chunk has
+    // been drained) and run the fused epilogue as a compact rolled loop: one warp per output column,
+    // 16 bytes per lane.  Keeping the epilogue out of the 128-fold unrolled register code matters:
+    // straight-line code that long is fetched once per tile and stalls on instruction fetch.
+    float* tile = reinterpret_cast<float*>(smem);
+    {
+      const int m_local = quarter * 32 + lane;
+#pragma unroll
+      for (int jx = 0; jx < kCols; ++jx) tile[(col0 + jx) * kTilePitch + m_local] = sum[jx];
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kEpiWarps * 32) : "memory");
+    if (ok) {
       const int64_t c_shift = (gridDim.y > 1) ? static_cast<int64_t>(blockIdx.y) * prob.split_stride : 0;
-      constexpr int kBatch = 8;
-#pragma unroll
-      for (int j0 = 0; j0 < kCols; j0 += kBatch) {
-        float old0[kBatch], old1[kBatch];
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-          const int n = n0 + col0 + j0 + u;
-          old0[u] = old1[u] = 0.0f;
-          if (n < prob.N && !(prob.symmetric && n > m)) epilogue_prefetch<MODE>(prob, c_shift, m, n, old0[u], old1[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < kBatch; ++u) {
-          const int n = n0 + col0 + j0 + u;
-          if (n < prob.N && !(prob.symmetric && n > m))
-            epilogue_finish<MODE>(prob, c_shift, m, n, sum[j0 + u], old0[u], old1[u]);
-        }
-      }
+      run_epilogue<BN, MODE>(prob, tile, m0, n0, ew, lane, c_shift);
     }
   }
 

@@ -7,22 +7,19 @@ namespace soapb200 {
 
 constexpr int kQrPanelWidth = 128;     // columns factored per panel (also the GEMM K of the updates)
 constexpr int kQrRowsPerCta = 256;     // rows of the panel held in one CTA's shared memory
-constexpr int kQrMaxRows = 148 * kQrRowsPerCta;
+constexpr int kQrMaxRows = 148 * kQrRowsPerCta;  // one CTA per SM at most (cooperative launch)
 
 // Factor one panel: the r x b matrix given as hi/lo planes (column-major, pitch ldp) is reduced by
 // b Householder reflectors H_c = I - tau_c v_c v_c^T (v_c[c] = 1, zeros above).
-// Outputs: V as planes (r x b, unit lower trapezoid, pitch ldv), V^T as planes (b x r, pitch ldvt),
-// tau[b], and S[b x b] (column-major) with S[j, c] = v_j^T v_c for j < c (input of larft).
+// Outputs, all as operand planes unless noted: V (r x b, unit lower trapezoid, pitch ldv), V^T
+// (b x r, pitch ldvt), tau[b] (plain), and the triangular factor of the compact WY form
+// H_0 ... H_{b-1} = I - V T V^T in both orientations (T and T^T, b x b, pitch ldt).
 // `exchange` is 8-byte-aligned scratch of at least 4 * (gridsize + 1) * 128 floats that persists
-// between calls; `status` is the device status word a timed-out exchange reports to.  Cooperative launch.
+// between calls; `status` is the device status word a timed-out exchange reports to.  Cooperative
+// launch of ceil(r / 256) CTAs.
 void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, float* v_hi, float* v_lo, int64_t ldv,
-              float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* S, float* exchange, int* status,
-              cudaStream_t stream);
-
-// Triangular factor of the compact WY form H_0 ... H_{b-1} = I - V T V^T from S and tau; T (b x b,
-// upper triangular) is written as operand planes in both orientations (pitch ldt each).
-void qr_larft(const float* S, const float* tau, int b, float* t_hi, float* t_lo, float* tt_hi, float* tt_lo, int64_t ldt,
-              cudaStream_t stream);
+              float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* t_hi, float* t_lo, float* tt_hi, float* tt_lo,
+              int64_t ldt, float* exchange, int* status, cudaStream_t stream);
 
 // planes <- sum over `splits` partial matrices (rows x cols, column-major pitch ld, `stride` floats apart).
 void sum_partials_to_planes(const float* partials, int splits, int64_t stride, int64_t ld, float* hi, float* lo,

@@ -4,8 +4,7 @@
 ``A[:, order]``, the contract of the reference's ``slate_qr_float`` (``geqrf`` + ``unmqr`` on an
 identity, ``src/soap_tp/csrc/slate_bindings.cpp:125-189``).  Per 128-column panel:
 
-    panel kernel (cooperative, panel resident in shared memory)  -> V, V^T planes, tau, V^T V
-    larft kernel                                                  -> T, T^T planes
+    panel kernel (cooperative, panel resident in registers)      -> V, V^T, T, T^T planes, tau
     Z = T V^T                      (3xTF32 tcgen05 GEMM, K = 128)
     W = V^T C_trailing             (split-K GEMM, partials summed in fixed order -> deterministic)
     C_trailing -= Z^T W            (GEMM whose epilogue read-modify-writes the operand planes)
@@ -92,14 +91,12 @@ def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = N
         nc = n - j0 - bw
         panel, v, vt = C.sub(j0, j0, r, bw), V.sub(j0, j0, r, bw), ws["Vt"][p]
         tau = ws["tau"][j0:]
-        _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(), v.ld,
-                    vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), ws["S"].data_ptr(),
-                    ws["exchange"].data_ptr(), k.status_word(device).data_ptr(), stream())
-        k._count("qr_panel_kernel")
         T, Tt = ws["T"][p], ws["Tt"][p]
-        _C.qr_larft(ws["S"].data_ptr(), tau.data_ptr(), bw, T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(),
-                    Tt.lo.data_ptr(), T.ld, stream())
-        k._count("larft_kernel")
+        _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(), v.ld,
+                    vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(), T.lo.data_ptr(),
+                    Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                    k.status_word(device).data_ptr(), stream())
+        k._count("qr_panel_kernel")
         if nc > 0:
             t_op = k.Planes(Tt.hi, Tt.lo, bw, bw, Tt.ld)
             vt_op = vt.sub(0, 0, bw, r)

@@ -48,6 +48,7 @@ class DenseSOAP:
         self.exp_avg = zeros(rows, columns)       # parameter space
         self.exp_avg_sq = zeros(rows, columns)    # rotated space
         self.step_count = 0
+        self.profile = False   # emit SOAP_PROFILE taps with impl "reference" (needs SOAP_PROFILE=1)
         self.qr_calls = 0
         self.last_orders: Optional[Tuple[Tensor, Tensor]] = None
 
@@ -77,24 +78,55 @@ class DenseSOAP:
     def step(self, gradient: Tensor) -> Tensor:
         """Consume one full gradient; return the normalised update (before learning rate)."""
         G = gradient.to(dtype=self.dtype, device=self.device)
+        tap = self._tap
         if self.QL is None:
+            tap("gradient", 0, G)
             self._update_grams(G)
+            tap("left_preconditioner", 0, self.L)
+            tap("right_preconditioner", 0, self.R)
             _, self.QL = self.eigenbasis_descending(self.L)
             _, self.QR = self.eigenbasis_descending(self.R)
+            tap("left_basis", 0, self.QL)
+            tap("right_basis", 0, self.QR)
+            tap("returned_update", 0, torch.zeros_like(G))
             return torch.zeros_like(G)
         self.step_count += 1
         t = self.step_count
+        tap("gradient", t, G)
+        for name, value in (("left_preconditioner", self.L), ("right_preconditioner", self.R),
+                            ("left_basis", self.QL), ("right_basis", self.QR)):
+            tap(name, t, value)
         rotated = self.QL.T @ G @ self.QR
+        tap("projected_gradient", t, rotated)
         self.exp_avg.mul_(self.beta1).add_(G, alpha=1.0 - self.beta1)
         self.exp_avg_sq.mul_(self.beta2).addcmul_(rotated, rotated, value=1.0 - self.beta2)
         denominator = self.exp_avg_sq.sqrt().add_(self.eps)
         rotated_momentum = self.QL.T @ self.exp_avg @ self.QR
         scale = math.sqrt(1.0 - self.beta2**t) / (1.0 - self.beta1**t)
-        update = (self.QL @ (rotated_momentum / denominator) @ self.QR.T) * scale
+        coordinate_update = rotated_momentum / denominator * scale
+        update = self.QL @ coordinate_update @ self.QR.T
+        tap("momentum_after_adam", t, rotated_momentum)
+        tap("variance_after_adam", t, self.exp_avg_sq)
+        tap("coordinate_update", t, coordinate_update)
+        tap("returned_update", t, update)
         self._update_grams(G)
+        tap("left_preconditioner_after_step", t, self.L)
+        tap("right_preconditioner_after_step", t, self.R)
         if t % self.interval == 0:
             self._refresh()
+        tap("left_basis_after_step", t, self.QL)
+        tap("right_basis_after_step", t, self.QR)
+        tap("momentum_after_step", t, self.QL.T @ self.exp_avg @ self.QR)
+        tap("variance_after_step", t, self.exp_avg_sq)
         return update
+
+    def _tap(self, stage: str, step: int, tensor: Tensor) -> None:
+        if not self.profile:
+            return
+        from ..profiling import emit_profile_tensor, profile_enabled
+
+        if profile_enabled(step):
+            emit_profile_tensor(stage, step, tensor.to(torch.float32), impl="reference")
 
 
 def relative_l2(actual: Tensor, expected: Tensor) -> float:
