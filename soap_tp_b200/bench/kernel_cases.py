@@ -1,0 +1,106 @@
+#!/usr/bin/env python3
+"""Run ONE kernel-level case a few times: the unit that gets profiled.
+
+    python -m soap_tp_b200.bench.kernel_cases gemm --size 4096 [--mode store|split|adam|ema]
+    python -m soap_tp_b200.bench.kernel_cases qr --size 4096
+    python -m soap_tp_b200.bench.kernel_cases panel --rows 4096
+    python -m soap_tp_b200.bench.kernel_cases update --size 4096      # QR trailing update (K = 128, planes RMW)
+    python -m soap_tp_b200.bench.kernel_cases adam --size 8192
+    python -m soap_tp_b200.bench.kernel_cases split --size 8192
+
+Each case allocates a few hundred MB at most, launches the kernel ``--repeats`` times and prints
+the CUDA-event time per launch, so the same command line serves for timing and, under ``ncu -k
+regex:<kernel> -c 1``, for a bounded profile capture.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def timed(fn, repeats: int) -> float:
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(repeats):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / repeats * 1e3
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("case", choices=("gemm", "qr", "panel", "update", "adam", "split"))
+    parser.add_argument("--size", type=int, default=4096)
+    parser.add_argument("--rows", type=int, default=4096)
+    parser.add_argument("--mode", default="store")
+    parser.add_argument("--repeats", type=int, default=3)
+    args = parser.parse_args(argv)
+
+    from ..engine import kernels as k
+    from ..engine import qr
+
+    n = args.size
+    device = torch.device("cuda", torch.cuda.current_device())
+    generator = torch.Generator(device=device).manual_seed(0)
+    rand = lambda *shape: torch.randn(*shape, generator=generator, device=device)
+    if args.case == "gemm":
+        a, b = k.split_planes(rand(n, n)), k.split_planes(rand(n, n))
+        out = torch.zeros(n, n, device=device).T
+        if args.mode == "store":
+            fn = lambda: k.gemm(a, b, out=out)
+        elif args.mode == "ema":
+            fn = lambda: k.gemm(a, a, out=out, alpha=0.05, beta=0.95, symmetric=True)
+        elif args.mode == "split":
+            planes = k.Planes.empty(n, n, device)
+            fn = lambda: k.gemm(a, b, mode=k.EPI_SPLIT, out_planes=planes)
+        else:
+            planes = k.Planes.empty(n, n, device)
+            momentum, variance = torch.zeros(n, n, device=device).T, torch.zeros(n, n, device=device).T
+            adam = dict(beta1=0.95, beta2=0.95, eps=1e-8, bias_correction1=0.5, bias_correction2=0.5)
+            fn = lambda: k.gemm(a, b, mode=k.EPI_ADAM, out_planes=planes, momentum=momentum, variance=variance, adam=adam)
+        us = timed(fn, args.repeats)
+        print(f"gemm_tf32x3 {args.mode} {n}^3: {us:.1f} us/launch, {2 * n**3 / us / 1e6:.1f} TFLOP/s fp32-equivalent "
+              f"({6 * n**3 / us / 1e6:.1f} TFLOP/s of tf32 MMA issued)")
+    elif args.case == "qr":
+        matrix, Q = rand(n, n).T, torch.empty(n, n, device=device).T
+        us = timed(lambda: qr.householder_qr(matrix.clone(), Q), args.repeats)
+        print(f"householder_qr {n}: {us / 1e3:.2f} ms")
+    elif args.case in ("panel", "update"):
+        ws = qr._workspace(max(n, args.rows), device)
+        k.split_planes(rand(max(n, args.rows), max(n, args.rows)), out=ws["C"])
+        if args.case == "panel":
+            r = args.rows
+            panel, v, vt, T, Tt = ws["C"].sub(0, 0, r, 128), ws["V"].sub(0, 0, r, 128), ws["Vt"][0], ws["T"][0], ws["Tt"][0]
+            fn = lambda: k._C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, 128, v.hi.data_ptr(),
+                                       v.lo.data_ptr(), v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld,
+                                       ws["tau"].data_ptr(), T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(),
+                                       Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                                       k.status_word(device).data_ptr(), k._stream())
+            print(f"qr_panel rows={r}: {timed(fn, args.repeats):.1f} us/launch")
+        else:
+            k.split_planes(rand(n, n), out=ws["V"])
+            z, w = ws["V"].sub(0, 0, 128, n), ws["V"].sub(128, 0, 128, n - 128)
+            trailing = ws["C"].sub(0, 128, n, n - 128)
+            fn = lambda: k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=trailing, alpha=-1.0, beta=1.0)
+            us = timed(fn, args.repeats)
+            print(f"trailing update {n} x {n - 128}, K=128: {us:.1f} us/launch, "
+                  f"{n * (n - 128) * 16 / us / 1e6:.2f} TB/s of plane traffic")
+    elif args.case == "adam":
+        g, m, v = (torch.rand(n, n, device=device).T for _ in range(3))
+        us = timed(lambda: k.adam_update(g, m, v, 0.9, 0.99, 1e-8, 0.5, 0.5), args.repeats)
+        print(f"adam {n}^2: {us:.1f} us/launch, {n * n * 24 / us / 1e6:.2f} TB/s")
+    else:
+        source, planes = rand(n, n), k.Planes.empty(n, n, device)
+        us = timed(lambda: k.split_planes(source, out=planes, transpose=True), args.repeats)
+        print(f"split_planes (transposing) {n}^2: {us:.1f} us/launch, {n * n * 12 / us / 1e6:.2f} TB/s")
+    k.check_status()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -58,6 +58,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     BUILD.mkdir(parents=True, exist_ok=True)
     common = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr", *ARCH_FLAGS, *_includes()]
+    if os.environ.get("SOAP_GEMM_BK"):
+        common += [f"-DSOAP_GEMM_BK={int(os.environ['SOAP_GEMM_BK'])}"]
     if verbose:
         common += ["-Xptxas", "-v"]
 

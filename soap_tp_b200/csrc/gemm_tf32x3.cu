@@ -37,19 +37,29 @@ namespace soapb200 {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kBK = 32;          // 32 fp32 = one 128-byte swizzle row
+#ifndef SOAP_GEMM_BK
+#define SOAP_GEMM_BK 32
+#endif
+// K extent of one pipeline stage: 32 fp32 = one 128-byte swizzle row (two 96 KB stages for 256-wide
+// tiles) or 16 fp32 = one 64-byte swizzle row (four 48 KB stages).  Both were measured at 8192^3; the
+// deeper pipeline of the 64-byte variant did not help (4.23 ms against 4.15 ms), because the kernel
+// is bound by the L2 -> shared-memory traffic of the four operand planes, not by load latency.
+constexpr int kBK = SOAP_GEMM_BK;
+static_assert(kBK == 16 || kBK == 32, "one swizzle row per k-block: 64 or 128 bytes");
+constexpr int kRowBytes = kBK * 4;
 constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each owning half of the tile's columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 // The tensor core adds into its fp32 accumulator with truncation, so an accumulation that runs over
 // the whole K extent drifts linearly in K (measured 6e-5 relative at K = 8192).  The accumulator is
 // therefore drained every kPromote k-blocks: the epilogue warps add it, round-to-nearest, into a
 // running sum held in registers while the tensor core fills the other TMEM buffer.
-constexpr int kPromote = 2;      // k-blocks (of 32) accumulated inside TMEM before promotion
+constexpr int kPromote = 64 / kBK;  // k-blocks (64 elements of K) accumulated inside TMEM before promotion
 
 template <int BN>
 struct TileConfig {
   static constexpr int kStageBytes = 2 * (kBM + BN) * kBK * 4;
-  static constexpr int kStages = (BN == 256) ? 2 : 3;
+  static constexpr int kStagesFit = (196 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 6 ? 6 : kStagesFit;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers (ping-pong)
   static constexpr int kColsPerThread = BN / 2;
@@ -323,9 +333,9 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
       mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
       const int k0 = (kb_first + kb) * kBK;
       tma_load_2d(stage, &maps.a_hi, &full_bar[s], k0, m0);
-      tma_load_2d(stage + kBM * 128, &maps.a_lo, &full_bar[s], k0, m0);
-      tma_load_2d(stage + 2 * kBM * 128, &maps.b_hi, &full_bar[s], k0, n0);
-      tma_load_2d(stage + 2 * kBM * 128 + BN * 128, &maps.b_lo, &full_bar[s], k0, n0);
+      tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], k0, m0);
+      tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], k0, n0);
+      tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], k0, n0);
     }
     if (*abort_flag) {
       // give copies that are still in flight time to land before the CTA's shared memory is released
@@ -352,10 +362,10 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t stage = smem_u32(smem + s * Cfg::kStageBytes);
-        const uint64_t a_hi = umma_desc_kmajor_sw128(stage);
-        const uint64_t a_lo = umma_desc_kmajor_sw128(stage + kBM * 128);
-        const uint64_t b_hi = umma_desc_kmajor_sw128(stage + 2 * kBM * 128);
-        const uint64_t b_lo = umma_desc_kmajor_sw128(stage + 2 * kBM * 128 + BN * 128);
+        const uint64_t a_hi = umma_desc_kmajor<kRowBytes>(stage);
+        const uint64_t a_lo = umma_desc_kmajor<kRowBytes>(stage + kBM * kRowBytes);
+        const uint64_t b_hi = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes);
+        const uint64_t b_lo = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes + BN * kRowBytes);
 #pragma unroll
         for (int k = 0; k < kBK / 8; ++k) {
           const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);  // 8 tf32 = 32 bytes along the swizzle row
@@ -454,7 +464,8 @@ CUtensorMap make_operand_map(const float* base, int64_t K, int64_t rows, int64_t
   cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t elem[2] = {1, 1};
   CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
-                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   kRowBytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(res));
   return map;

@@ -128,12 +128,16 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // is exactly 128 bytes (32 fp32): rows are 128 B apart, 8-row groups 1024 B apart.
 //   start address >> 4 | LBO (ignored for swizzled K-major, canonical value 1) << 16 |
 //   SBO = 1024 >> 4 << 32 | descriptor version 1 << 46 | layout SWIZZLE_128B (2) << 61
-__device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
+// The same with a 64-byte-swizzled box of 16 fp32: rows 64 B apart, 8-row groups 512 B apart, layout
+// SWIZZLE_64B (4).
+template <int RowBytes>
+__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr) {
+  static_assert(RowBytes == 128 || RowBytes == 64, "one swizzle row per k-block");
   uint64_t desc = static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   desc |= static_cast<uint64_t>(1) << 16;
-  desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+  desc |= static_cast<uint64_t>((8 * RowBytes) >> 4) << 32;
   desc |= static_cast<uint64_t>(1) << 46;
-  desc |= static_cast<uint64_t>(2) << 61;
+  desc |= static_cast<uint64_t>(RowBytes == 128 ? 2 : 4) << 61;
   return desc;
 }
 // kind::tf32, fp32 accumulator, both operands K-major, no negation, dense.

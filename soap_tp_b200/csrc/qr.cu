@@ -60,6 +60,8 @@ struct PanelArgs {
   unsigned long long* exchange;  // [2][ctas + 1][kB] packed {value, sequence} words
   unsigned int epoch;            // distinguishes this launch's words from stale ones in `exchange`
   int* status;
+  long long* trace;              // optional: clock64 stamps of CTA 0 at column 64 (diagnostics), may be null
+  int debug_skip;                // diagnostics only: bit 0 skips the T column, bit 1 the pivot-row bookkeeping
 };
 
 // One 64-bit word carries a value and the sequence number that says which step it belongs to, so a
@@ -106,34 +108,59 @@ __device__ __forceinline__ float take_pivot_entry(float (&P)[64], int k, bool cl
 }
 #undef SOAP_PIVOT_CASE
 
+// Column cc of the compact-WY factor: T[0:cc, cc] = -tau_cc * T[0:cc, 0:cc] * S[0:cc, cc], T[cc, cc] = tau_cc.
+// Called by all 512 threads of a CTA: four threads share a row, two independent accumulators each.
+__device__ __forceinline__ void t_column(float (*T)[kPitch], const float* scol, const float* taus, int cc, int t) {
+  const int i = t >> 2, part = t & 3;
+  float a0 = 0.f, a1 = 0.f;
+  if (i < cc) {
+    int k = i + part;
+    for (; k + 4 < cc; k += 8) {
+      a0 = fmaf(T[i][k], scol[k], a0);
+      a1 = fmaf(T[i][k + 4], scol[k + 4], a1);
+    }
+    if (k < cc) a0 = fmaf(T[i][k], scol[k], a0);
+  }
+  float acc = a0 + a1;
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  if (part == 0) {
+    if (i < cc) T[i][cc] = -taus[cc] * acc;
+    else if (i == cc) T[i][cc] = taus[cc];
+  }
+}
+
 constexpr int kMaxPollWords = 10;   // words one thread requests per polling round (40 CTAs' worth per round)
 
-// Panel factorisation.  Thread (j, q) keeps rows q*64 .. q*64+63 of column j of its CTA's 256-row
-// slab in REGISTERS for the whole panel; shared memory only carries the pivot column.  A column step
-// is: dot products of the pivot column with every column (register sweep) -> one all-to-all exchange
-// of the partial sums, all polls of a step in flight together -> Householder scalars -> rank-1
-// update (register sweep).  While CTA 0 waits for the exchange its idle warps build the compact-WY
-// triangular factor T column by column, so no separate pass over V is needed for it.
+constexpr int kSlice = 64 + 4;   // floats between the four 64-row slices of the pivot column in shared memory
+                                 // (the 16-byte skew keeps the four lanes of a column on different banks)
+
+// Panel factorisation.  The four lanes 4j .. 4j+3 of a warp own column j of the CTA's 256-row slab:
+// lane q keeps rows q*64 .. q*64+63 in REGISTERS for the whole panel, so per-column reductions are
+// two warp shuffles and shared memory only carries the pivot column.  A column step is
+//   sweep 1  dot products of the pivot column with every column            (registers + shuffles)
+//   exchange partial sums of all CTAs, every poll of the step in flight together; meanwhile CTA 0
+//            builds column c-1 of the compact-WY factor T
+//   barrier, Householder scalars (every thread), sweep 2: rank-1 update, next pivot column published
+//   barrier
+// i.e. two CTA barriers and one all-to-all per column.
 __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a) {
-  __shared__ __align__(16) float xcol[kRows];   // pivot column, zero at and above rows already eliminated
-  __shared__ float red[4][kB];
-  __shared__ float gathered[4][kB];             // per-quarter sums of the other CTAs' partial dot products
-  __shared__ float dots[kB];
-  __shared__ float pivot_row[kB];
-  __shared__ float scales[kB];
+  __shared__ __align__(16) float xcol[2][4 * kSlice];   // pivot column (double buffered); rows above the pivot are zero
+  __shared__ float pivot_stats[2][2];                   // {alpha, |x|^2} of the pivot column (double buffered)
   __shared__ float taus[kB];
-  __shared__ float scol[kB];                    // column c of S = V^T V (entries above the diagonal)
+  __shared__ float scol[kB];                            // column c of S = V^T V (entries above the diagonal)
+  __shared__ float pivot_row_local[kB];                 // single-CTA launches: row c without a trip through memory
   __shared__ int abort_flag;
   extern __shared__ float dyn[];
   float (*T)[kPitch] = reinterpret_cast<float (*)[kPitch]>(dyn);   // CTA 0: compact-WY factor; all: output staging
 
   const int t = threadIdx.x;
-  const int j = t & (kB - 1);
-  const int q = t >> 7;
+  const int j = t >> 2;                  // column owned by this lane quad
+  const int q = t & 3;                   // 64-row slice within the CTA's slab
   const int row0 = blockIdx.x * kRows;
   const int rows_here = min(kRows, a.r - row0);
   const int ctas = gridDim.x;
-  const int my_first = q * 64;           // first local row held by this thread
+  const int my_first = q * 64;
 
   float P[64];
 #pragma unroll
@@ -146,32 +173,31 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
     }
     P[k] = v;
   }
-  if (t < kB) {
-    scales[t] = 1.f;
-    taus[t] = 0.f;
-  }
+  if (t < kB) taus[t] = 0.f;
   if (t == 0) abort_flag = 0;
   if (blockIdx.x == 0)
     for (int idx = t; idx < kB * kPitch; idx += kPanelThreads) dyn[idx] = 0.f;
   if (j == 0) {
 #pragma unroll
-    for (int k = 0; k < 64; ++k) xcol[my_first + k] = P[k];   // column 0, pivot row 0: nothing above it
+    for (int k = 0; k < 64; ++k) xcol[0][q * kSlice + k] = P[k];   // column 0, pivot row 0: nothing above it
   }
   __syncthreads();
 
   const int reflectors = min(a.b, a.r);
   const unsigned int seq_base = a.epoch * 256u;
+  float my_scale = 1.f;                  // 1 / (alpha - beta) of this lane's column once it has been a pivot
 
   for (int c = 0; c < reflectors; ++c) {
     const int parity = c & 1;
     const unsigned int seq = seq_base + static_cast<unsigned int>(c) + 1u;
     unsigned long long* slots = a.exchange + static_cast<int64_t>(parity) * (ctas + 1) * kB;
     const int pivot_local = c - row0;                   // local index of the pivot row (may be outside this CTA)
-    const bool pivot_mine = pivot_local >= my_first && pivot_local < my_first + 64;   // warp-uniform
-    // ---- sweep 1: dot products of the pivot column with every column ----
+    const bool pivot_mine = pivot_local >= my_first && pivot_local < my_first + 64;
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[7] = clock64();
+    // ---- sweep 1: dot product of the pivot column with this lane's slice of column j ----
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
     {
-      const float4* x4 = reinterpret_cast<const float4*>(&xcol[my_first]);
+      const float4* x4 = reinterpret_cast<const float4*>(&xcol[parity][q * kSlice]);
 #pragma unroll
       for (int k4 = 0; k4 < 16; ++k4) {
         const float4 x = x4[k4];
@@ -181,34 +207,26 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
         acc3 = fmaf(P[4 * k4 + 3], x.w, acc3);
       }
     }
-    red[q][j] = (acc0 + acc1) + (acc2 + acc3);
-    if (pivot_mine) {
-      // Row c of the panel.  Right of the pivot it only holds R entries nobody reads again: they are
-      // zeroed so that later pivot columns leave the registers already masked.
-      const float row_value = take_pivot_entry(P, pivot_local - my_first, j > c);
-      if (ctas > 1) ll_publish(&slots[static_cast<int64_t>(ctas) * kB + j], row_value, seq);
-      else pivot_row[j] = row_value;
+    float partial = (acc0 + acc1) + (acc2 + acc3);
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[8] = clock64();
+    partial += __shfl_xor_sync(0xffffffffu, partial, 1);
+    partial += __shfl_xor_sync(0xffffffffu, partial, 2);     // all four lanes: this CTA's partial dot for column j
+    float row_value = 0.f;                                    // entry (c, j) of the panel, on the lane that holds it
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[1] = clock64();
+    if (pivot_mine && !(a.debug_skip & 2)) row_value = take_pivot_entry(P, pivot_local - my_first, false);
+    if (ctas > 1) {
+      if (q == 0) ll_publish(&slots[static_cast<int64_t>(blockIdx.x) * kB + j], partial, seq);
+      if (pivot_mine) ll_publish(&slots[static_cast<int64_t>(ctas) * kB + j], row_value, seq);
     }
-    __syncthreads();                                                              // B1
-    if (t < kB && ctas > 1)
-      ll_publish(&slots[static_cast<int64_t>(blockIdx.x) * kB + t], (red[0][t] + red[1][t]) + (red[2][t] + red[3][t]), seq);
-    // ---- CTA 0, warps 8..15, while the published words travel: column c-1 of T ----
-    if (blockIdx.x == 0 && c > 0 && t >= 2 * kB) {
-      const int cc = c - 1;
-      const int i = (t - 2 * kB) >> 1, part = t & 1;      // two threads per row of T
-      float acc = 0.f;
-      if (i < cc)
-        for (int k = i + part; k < cc; k += 2) acc = fmaf(T[i][k], scol[k], acc);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (part == 0) {
-        if (i < cc) T[i][cc] = -taus[cc] * acc;
-        else if (i == cc) T[i][cc] = taus[cc];
-      }
-    }
-    // ---- exchange: quarter q of the threads polls the words of CTAs q, q+4, q+8, ... (and of the pivot
-    //      row, index `ctas`); all words of a round are requested before any is inspected ----
+    // ---- CTA 0, while the published words travel: column c-1 of T (four threads per row) ----
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[2] = clock64();
+    if (blockIdx.x == 0 && c > 0 && !(a.debug_skip & 1)) t_column(T, scol, taus, c - 1, t);
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[3] = clock64();
+    // ---- exchange: lane q polls the words of CTAs q, q+4, q+8, ... (index `ctas` = the pivot row) ----
+    float total = partial, prow = row_value;
     if (ctas > 1) {
       float part = 0.f;
+      prow = 0.f;
       bool failed = false;
       for (int base = 0; base <= ctas && !failed; base += 4 * kMaxPollWords) {
         unsigned long long words[kMaxPollWords];
@@ -233,28 +251,38 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
         for (int u = 0; u < kMaxPollWords; ++u) {
           const int g = base + q + 4 * u;
           if (g < ctas) part += __uint_as_float(static_cast<unsigned int>(words[u]));
-          else if (g == ctas) pivot_row[j] = __uint_as_float(static_cast<unsigned int>(words[u]));
+          else if (g == ctas) prow = __uint_as_float(static_cast<unsigned int>(words[u]));
         }
       }
       if (failed) {
         abort_flag = 1;
         atomicCAS(a.status, 0, 4);
       }
-      gathered[q][j] = part;
+      // fixed-shape reduction over the four lanes: identical on every CTA
+      const float p1 = __shfl_xor_sync(0xffffffffu, part, 1);
+      const float pair = (q & 1) ? (p1 + part) : (part + p1);
+      const float p2 = __shfl_xor_sync(0xffffffffu, pair, 2);
+      total = (q & 2) ? (p2 + pair) : (pair + p2);
+      prow += __shfl_xor_sync(0xffffffffu, prow, 1);
+      prow += __shfl_xor_sync(0xffffffffu, prow, 2);          // exactly one lane contributed a non-zero word
+    } else {
+      if (pivot_mine) pivot_row_local[j] = row_value;
     }
-    __syncthreads();                                                              // B2
+    if (ctas > 1 && j == c && q == 0) {
+      pivot_stats[parity][0] = prow;
+      pivot_stats[parity][1] = total;
+    }
+    if (ctas == 1 && j == c && q == 0) pivot_stats[parity][1] = total;
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[6] = clock64();
+    __syncthreads();                                                              // barrier 1
+    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[0] = clock64();
     if (abort_flag) break;
-    if (t < kB) {
-      const float total = (ctas > 1) ? (gathered[0][t] + gathered[1][t]) + (gathered[2][t] + gathered[3][t])
-                                     : (red[0][t] + red[1][t]) + (red[2][t] + red[3][t]);
-      const float s = (t < c) ? scales[t] : 1.f;        // finished columns are kept unscaled
-      dots[t] = total * s;
-      pivot_row[t] *= s;
-      if (t == 0 && pivot_local >= 0 && pivot_local < kRows) xcol[pivot_local] = 0.f;   // v_c[c] = 1 only touches dead R entries
-    }
-    __syncthreads();                                                              // B3
-    const float alpha = pivot_row[c];
-    const float normsq = dots[c];
+    if (ctas == 1) prow = pivot_row_local[j];
+    // finished columns are kept unscaled in the registers: apply their scale to the two dot-like values
+    const float dots_j = total * ((j < c) ? my_scale : 1.f);
+    const float prow_j = prow * ((j < c) ? my_scale : 1.f);
+    const float alpha = (ctas == 1) ? pivot_row_local[c] : pivot_stats[parity][0];
+    const float normsq = pivot_stats[parity][1];
     const float tail = normsq - alpha * alpha;
     float tau = 0.f, scale = 0.f;
     if (tail > 0.f && normsq > 0.f) {
@@ -262,53 +290,45 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
       tau = (beta - alpha) * __frcp_rn(beta);
       scale = __frcp_rn(alpha - beta);
     }
-    const float w = pivot_row[j] + scale * (dots[j] - alpha * pivot_row[j]);   // v_c^T column_j
+    const float w = prow_j + scale * (dots_j - alpha * prow_j);                   // v_c^T column_j
+    if (j == c) my_scale = scale;
     if (blockIdx.x == 0 && q == 0) {
       if (j < c) scol[j] = w;
       if (j == c) {
         taus[c] = tau;
         a.tau[c] = tau;
-        scales[c] = scale;
       }
-    } else if (q == 0 && j == c) {
-      scales[c] = scale;
     }
     // ---- sweep 2: rank-1 update of the columns right of the pivot, publish the next pivot column ----
-    if (j > c && tau != 0.f) {
-      const float tws = tau * w * scale;               // v_i = scale * x_i below the pivot, xcol is zero elsewhere
-      const float4* x4 = reinterpret_cast<const float4*>(&xcol[my_first]);
+    if (j > c) {
+      if (tau != 0.f) {
+        const float tws = tau * w * scale;             // v_i = scale * x_i below the pivot
+        const float4* x4 = reinterpret_cast<const float4*>(&xcol[parity][q * kSlice]);
 #pragma unroll
-      for (int k4 = 0; k4 < 16; ++k4) {
-        const float4 x = x4[k4];
-        P[4 * k4 + 0] = fmaf(-tws, x.x, P[4 * k4 + 0]);
-        P[4 * k4 + 1] = fmaf(-tws, x.y, P[4 * k4 + 1]);
-        P[4 * k4 + 2] = fmaf(-tws, x.z, P[4 * k4 + 2]);
-        P[4 * k4 + 3] = fmaf(-tws, x.w, P[4 * k4 + 3]);
+        for (int k4 = 0; k4 < 16; ++k4) {
+          const float4 x = x4[k4];
+          P[4 * k4 + 0] = fmaf(-tws, x.x, P[4 * k4 + 0]);
+          P[4 * k4 + 1] = fmaf(-tws, x.y, P[4 * k4 + 1]);
+          P[4 * k4 + 2] = fmaf(-tws, x.z, P[4 * k4 + 2]);
+          P[4 * k4 + 3] = fmaf(-tws, x.w, P[4 * k4 + 3]);
+        }
+      }
+      // Row c right of the pivot now only holds R entries nobody reads again: zero them so that later
+      // pivot columns leave the registers already masked above their pivot row.
+      if (pivot_mine && !(a.debug_skip & 2)) take_pivot_entry(P, pivot_local - my_first, true);
+      if (j == c + 1) {
+        float4* x4 = reinterpret_cast<float4*>(&xcol[parity ^ 1][q * kSlice]);
+#pragma unroll
+        for (int k4 = 0; k4 < 16; ++k4) x4[k4] = make_float4(P[4 * k4], P[4 * k4 + 1], P[4 * k4 + 2], P[4 * k4 + 3]);
       }
     }
-    __syncthreads();                                                              // B4: everyone is done reading xcol
-    if (j == c + 1) {   // rows above the new pivot were zeroed when their own pivot step finished
-      float4* x4 = reinterpret_cast<float4*>(&xcol[my_first]);
-#pragma unroll
-      for (int k4 = 0; k4 < 16; ++k4) x4[k4] = make_float4(P[4 * k4], P[4 * k4 + 1], P[4 * k4 + 2], P[4 * k4 + 3]);
-    }
-    __syncthreads();                                                              // B5
+    __syncthreads();                                                              // barrier 2
+    if (a.trace && blockIdx.x == 0 && t == 0 && (c == 64 || c == 63)) a.trace[c == 64 ? 4 : 5] = clock64();
   }
 
   // ---- CTA 0: last column of T, then T and T^T as operand planes ----
   if (blockIdx.x == 0 && !abort_flag) {
-    const int cc = reflectors - 1;
-    if (t >= 2 * kB) {
-      const int i = (t - 2 * kB) >> 1, part = t & 1;
-      float acc = 0.f;
-      if (i < cc)
-        for (int k = i + part; k < cc; k += 2) acc = fmaf(T[i][k], scol[k], acc);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (part == 0) {
-        if (i < cc) T[i][cc] = -taus[cc] * acc;
-        else if (i == cc) T[i][cc] = taus[cc];
-      }
-    }
+    t_column(T, scol, taus, reflectors - 1, t);
     __syncthreads();
     for (int idx = t; idx < kB * kB; idx += kPanelThreads) {
       const int r = idx & (kB - 1), cidx = idx >> 7;
@@ -326,21 +346,14 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
     __syncthreads();
   }
 
-  // ---- outputs: V^T (b x r) straight from registers, V (r x b) through a shared-memory transpose ----
-  const float my_scale = (j < reflectors) ? scales[j] : 0.f;
+  // ---- outputs: V (r x b) and V^T (b x r) through a shared-memory tile, one 64-row slice at a time ----
+  const float out_scale = (j < reflectors) ? my_scale : 0.f;
 #pragma unroll
   for (int k = 0; k < 64; ++k) {
-    const int i = my_first + k;
-    const int gi = row0 + i;
+    const int gi = row0 + my_first + k;
     float v = 0.f;
-    if (j < reflectors) v = (gi > j) ? P[k] * my_scale : (gi == j ? 1.f : 0.f);
+    if (j < reflectors) v = (gi > j) ? P[k] * out_scale : (gi == j ? 1.f : 0.f);
     P[k] = v;
-    if (i < rows_here && j < a.b) {
-      const float h = tf32_rn(v);
-      const int64_t off = j + static_cast<int64_t>(gi) * a.ldvt;
-      a.vt_hi[off] = h;
-      a.vt_lo[off] = v - h;
-    }
   }
   float (*stage)[kPitch] = T;   // 64 x 129 staging tile (T has been written out)
   for (int slice = 0; slice < 4; ++slice) {
@@ -351,7 +364,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
     }
     __syncthreads();
     for (int idx = t; idx < 64 * kB; idx += kPanelThreads) {
-      const int k = idx & 63, jj = idx >> 6;             // consecutive threads -> consecutive rows
+      const int k = idx & 63, jj = idx >> 6;             // consecutive threads -> consecutive rows (V)
       const int i = slice * 64 + k;
       if (i < rows_here && jj < a.b) {
         const float v = stage[k][jj];
@@ -359,6 +372,17 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
         const int64_t off = (row0 + i) + static_cast<int64_t>(jj) * a.ldv;
         a.v_hi[off] = h;
         a.v_lo[off] = v - h;
+      }
+    }
+    for (int idx = t; idx < 64 * kB; idx += kPanelThreads) {
+      const int jj = idx & (kB - 1), k = idx >> 7;       // consecutive threads -> consecutive columns (V^T)
+      const int i = slice * 64 + k;
+      if (i < rows_here && jj < a.b) {
+        const float v = stage[k][jj];
+        const float h = tf32_rn(v);
+        const int64_t off = jj + static_cast<int64_t>(row0 + i) * a.ldvt;
+        a.vt_hi[off] = h;
+        a.vt_lo[off] = v - h;
       }
     }
   }
@@ -400,7 +424,7 @@ inline int grid_for(int64_t total) {
 
 void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, float* v_hi, float* v_lo, int64_t ldv,
               float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* t_hi, float* t_lo, float* tt_hi, float* tt_lo,
-              int64_t ldt, float* exchange, int* status, cudaStream_t stream) {
+              int64_t ldt, float* exchange, int* status, cudaStream_t stream, long long* trace, int debug_skip) {
   if (r <= 0 || b <= 0) return;
   if (b > kB) throw std::invalid_argument("qr_panel: panel wider than 128 columns");
   if (r > kQrMaxRows) throw std::invalid_argument("qr_panel: more rows than one cooperative grid can hold");
@@ -415,7 +439,7 @@ void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, f
     configured = true;
   }
   PanelArgs args{p_hi, p_lo, ldp, r, b, v_hi, v_lo, ldv, vt_hi, vt_lo, ldvt, tau, t_hi, t_lo, tt_hi, tt_lo, ldt,
-                 reinterpret_cast<unsigned long long*>(exchange), epoch, status};
+                 reinterpret_cast<unsigned long long*>(exchange), epoch, status, trace, debug_skip};
   void* params[] = {&args};
   const int ctas = (r + kRows - 1) / kRows;
   // Cooperative launch: the CTAs exchange data through global memory while running, so all of them
