@@ -183,6 +183,10 @@ def run(args: argparse.Namespace) -> int:
                              basis_refresh_interval=args.refresh_interval, basis_implementation=basis)
 
         launches = kernels.total_launches
+        if args.stage_timing:
+            from soap_tp_b200.profiling import GLOBAL_STAGE_TIMER
+
+            GLOBAL_STAGE_TIMER.enabled = True
 
     def fence() -> None:
         dist.barrier()
@@ -203,6 +207,8 @@ def run(args: argparse.Namespace) -> int:
     fence()
 
     # ---- device-timed region ----
+    if args.impl == "ours" and args.stage_timing:
+        GLOBAL_STAGE_TIMER.reset()
     resident = [gradient_for(counter + i, rank, shard_shape, device, cache) for i in range(pool)]
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -218,6 +224,12 @@ def run(args: argparse.Namespace) -> int:
     device_ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
     dist.all_reduce(device_ms, op=dist.ReduceOp.MAX)
     launches_timed = launches() - launches_before
+    if args.impl == "ours" and args.stage_timing:
+        stages = GLOBAL_STAGE_TIMER.summary()
+        GLOBAL_STAGE_TIMER.enabled = False
+        if rank == 0:
+            print(json.dumps({"stage_ms_per_step_max_over_ranks": {n: round(v / args.steps, 3) for n, v in stages.items()}}),
+                  file=sys.stderr)
     clocks = sampler.stop() if rank == 0 else {}
     counter += args.steps
 

@@ -26,6 +26,7 @@ from torch import Tensor
 
 from ..layout import grid_coords, numroc, owned_indices
 from ..parallel.comm import Communicator, SymmetricSegment, get_communicator
+from ..profiling import GLOBAL_STAGE_TIMER as TIMER
 from . import factor
 from . import kernels as k
 
@@ -101,6 +102,7 @@ class GridEngine:
         self.pr, self.pc = grid_coords(self.rank, grid)
         self._planes: Dict[tuple, k.Planes] = {}
         self._basis_cache: Dict[tuple, dict] = {}
+        self._leader_tables: Dict[tuple, Tensor] = {}
 
     # ---- small helpers -----------------------------------------------------------------------
     def rows_of(self, n: int) -> int:
@@ -122,6 +124,15 @@ class GridEngine:
             found = k.Planes.empty(depth, cols, self.device)
             self._planes[key] = found
         return found
+
+    def leader_table(self, segment: SymmetricSegment, leader: int) -> Tensor:
+        """One-entry peer table that points at ``leader``'s copy of ``segment``."""
+        key = (segment.name, leader)
+        table = self._leader_tables.get(key)
+        if table is None:
+            table = torch.tensor([segment.peer_ptrs[leader]], dtype=torch.int64, device=self.device)
+            self._leader_tables[key] = table
+        return table
 
     def packed_segment(self, tag: str, shape) -> Tuple[SymmetricSegment, Tensor, Source]:
         """Symmetric staging buffer holding a packed block-cyclic matrix of global ``shape``."""
@@ -384,20 +395,76 @@ def _scatter_owned(e: GridEngine, dense: Tensor, packed: Tensor, size: int) -> N
         k.mark_written(packed)
 
 
+def _leader_of(job: int, jobs: int, world: int) -> int:
+    """Rank that runs job ``job`` of ``jobs`` independent dense factorisations."""
+    return (job * world) // jobs
+
+
+def _factor_on_leaders(e: GridEngine, jobs, run) -> None:
+    """Run independent dense factorisations concurrently, one per leader rank.
+
+    ``jobs`` is a list of ``(packed input, packed output, size, column_order)``.  Every rank stages
+    its part of every input; the leader of job ``i`` pulls the whole (column-permuted) matrix,
+    calls ``run(i, dense_input, dense_output)`` with this package's single-GPU kernels, and leaves
+    the dense result in a symmetric segment from which every rank then pulls the tiles it owns.
+    With two jobs (left and right basis) and at least two ranks the two factorisations overlap
+    completely; the factorisations are deterministic, so nothing has to be compared afterwards.
+    """
+    count = len(jobs)
+    sources = []
+    for index, (matrix, _, size, _) in enumerate(jobs):
+        sources.append(e.stage_packed(f"factor_in{index}", matrix, (size, size)))
+    e.comm.barrier()
+    results = []
+    for index, (matrix, output, size, order) in enumerate(jobs):
+        leader = _leader_of(index, count, e.world)
+        segment = e.comm.segment(f"factor_out{index}:{size}", size * size)
+        results.append((segment, leader))
+        if e.rank == leader:
+            dense_in = _gather_dense(e, sources[index], size, order)
+            dense_out = segment.local[: size * size].view(size, size).T
+            run(index, dense_in, dense_out)
+    e.comm.barrier()
+    for (matrix, output, size, order), (segment, leader) in zip(jobs, results):
+        table = e.leader_table(segment, leader)
+        source = Source(segment, KIND_BLOCK_CYCLIC, size, size, 1, 1, 1, 1, 1)
+        lr, lc = e.rows_of(size), e.cols_of(size)
+        if lr and lc:
+            _dist_gather_table(table, source, e.row_map(), e.col_map(), lr, lc, output[:lr, :lc])
+    e.comm.barrier()
+
+
+def _dist_gather_table(table: Tensor, src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, cols_out: int,
+                       out: Tensor) -> None:
+    """``dist_gather`` with an explicit peer table (here: a single entry, the leader's buffer)."""
+    d_i = out.stride(0) if out.shape[0] > 1 else 1
+    d_j = out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0])
+    k._C.dist_gather(table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
+                     map_i.p, map_i.P, map_i.nb, map_i.offset, 0, map_j.p, map_j.P, map_j.nb, map_j.offset, 0, 0,
+                     out.data_ptr(), 0, d_i, d_j, rows_out, cols_out, k._stream())
+    k._count("dist_gather_kernel")
+    k.mark_written(out)
+
+
+def qr_many(e: GridEngine, jobs) -> None:
+    """``jobs``: list of ``(packed matrix, packed Q, size, column_order)``; see :func:`_factor_on_leaders`."""
+    from ..ops.basis import count_qr_call
+
+    _factor_on_leaders(e, jobs, lambda index, dense_in, dense_out: factor.householder_qr(dense_in, dense_out))
+    # the leader's factorisation counted itself; the other ranks took part in the same collective call
+    for index in range(len(jobs)):
+        if _leader_of(index, len(jobs), e.world) != e.rank:
+            count_qr_call()
+
+
 def qr(matrix: Tensor, Q: Tensor, size: int, block_size: int, grid, column_order: Optional[Tensor] = None) -> Tensor:
     """Householder QR of the packed ``matrix`` (columns optionally permuted on the way in).
 
-    Every rank pulls the whole (permuted) matrix, factors it with the single-GPU blocked Householder
-    kernels and keeps the tiles it owns; the factorisation is deterministic, so all ranks agree.
+    One rank pulls the whole (permuted) matrix and factors it with the single-GPU blocked
+    Householder kernels; every rank then pulls the tiles of ``Q`` it owns from that rank.
     """
     e = engine_for(matrix.device, grid, block_size)
-    source = e.stage_packed("stage", matrix, (size, size))
-    e.comm.barrier()
-    dense = _gather_dense(e, source, size, column_order)
-    e.comm.barrier()
-    full_q = torch.empty((size, size), dtype=torch.float32, device=matrix.device).T
-    factor.householder_qr(dense, full_q)
-    _scatter_owned(e, full_q, Q, size)
+    qr_many(e, [(matrix, Q, size, column_order)])
     return Q
 
 
@@ -407,17 +474,34 @@ def power_iteration_qr(P: Tensor, Q: Tensor, work: Tensor, size: int, block_size
     return order
 
 
+def initialize_bases(e: GridEngine, jobs) -> None:
+    """``jobs``: list of ``(packed P, packed Q, size, eigenvalues, implementation)`` solved concurrently."""
+    scratch = {}
+
+    def run(index, dense_in, dense_out):
+        _, _, size, values, implementation = jobs[index]
+        work = torch.empty((size, size), dtype=torch.float32, device=e.device).T
+        factor.symmetric_eigenbasis(dense_in, dense_out, work, values, implementation)
+        scratch[index] = values
+
+    _factor_on_leaders(e, [(P, Q, size, None) for P, Q, size, _, _ in jobs], run)
+    # eigenvalues live on the leader; hand them to everybody through a small segment
+    for index, (_, _, size, values, _) in enumerate(jobs):
+        leader = _leader_of(index, len(jobs), e.world)
+        segment = e.comm.segment(f"eigenvalues{index}:{size}", size)
+        if e.rank == leader:
+            segment.local[:size].copy_(values)
+        e.comm.barrier()
+        table = e.leader_table(segment, leader)
+        out = values.view(size, 1)
+        _dist_gather_table(table, Source(segment, KIND_BLOCK_CYCLIC, size, 1, 1, 1, 1, 1, 1), IDENTITY, IDENTITY, size, 1, out)
+        e.comm.barrier()
+
+
 def initialize_basis(P: Tensor, Q: Tensor, work: Tensor, eigenvalues: Tensor, size: int, block_size: int, grid,
                      implementation: str) -> Tensor:
     e = engine_for(P.device, grid, block_size)
-    source = e.stage_packed("stage", P, (size, size))
-    e.comm.barrier()
-    dense = _gather_dense(e, source, size)
-    e.comm.barrier()
-    full_q = torch.empty((size, size), dtype=torch.float32, device=P.device).T
-    scratch = torch.empty((size, size), dtype=torch.float32, device=P.device).T
-    factor.symmetric_eigenbasis(dense, full_q, scratch, eigenvalues, implementation)
-    _scatter_owned(e, full_q, Q, size)
+    initialize_bases(e, [(P, Q, size, eigenvalues, implementation)])
     return Q
 
 
@@ -441,57 +525,92 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
     e = engine_for(gradient_shard.device, grid, block_size)
     rows, cols = global_shape
     device = gradient_shard.device
-    shard_source = e.stage_shard(gradient_shard, global_shape, shard_dim)
-    e.comm.barrier()
+    with TIMER.stage("stage_gradient", device):
+        shard_source = e.stage_shard(gradient_shard, global_shape, shard_dim)
+        e.comm.barrier()
 
     if initializing:
         _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
         _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right")
         e.comm.barrier()
-        for side, size in (("left", rows), ("right", cols)):
-            values = torch.empty(size, dtype=torch.float32, device=device)
-            initialize_basis(state[f"{side}_preconditioner"], state[f"{side}_basis"], state[f"{side}_work"], values,
-                             size, block_size, grid, implementation)
+        initialize_bases(e, [
+            (state[f"{side}_preconditioner"], state[f"{side}_basis"], size,
+             torch.empty(size, dtype=torch.float32, device=device), implementation)
+            for side, size in (("left", rows), ("right", cols))])
+        prepare_refresh(e, global_shape)
         state["step"] = 0
         return torch.zeros(gradient_shard.shape, dtype=torch.float32, device=device)
 
     step = int(state["step"]) + 1
-    left_plain, left_t = e.basis_panels(state["left_basis"], rows, "left")
-    right_plain, right_t = e.basis_panels(state["right_basis"], cols, "right")
+    with TIMER.stage("basis_panels", device):
+        left_plain, left_t = e.basis_panels(state["left_basis"], rows, "left")
+        right_plain, right_t = e.basis_panels(state["right_basis"], cols, "right")
     lr, lc = e.rows_of(rows), e.cols_of(cols)
     bias2 = 1.0 - beta2**step
     adam = dict(beta1=beta1, beta2=beta2, eps=eps / math.sqrt(bias2),
                 bias_correction1=1.0 - beta1**step, bias_correction2=bias2)
     # forward rotation straight from the tensor-parallel shards, Adam in the epilogue, update -> segment
-    _, u_view, u_source = e.packed_segment("update", global_shape)
-    x_panel = e.planes("x_panel", rows, e.rows_of(cols))   # X[:, my row class]; reused by the right Gram
-    dist_gather(shard_source, IDENTITY, e.row_map(), rows, e.rows_of(cols), planes=x_panel)
-    e.two_sided(shard_source, global_shape, left_plain, right_plain, gathered=x_panel, mode=k.EPI_ADAM,
-                          out=u_view[: max(1, lr), : max(1, lc)],
-                          momentum=state["momentum"][: max(1, lr), : max(1, lc)],
-                          variance=state["variance"][: max(1, lr), : max(1, lc)], adam=adam)
-    e.comm.barrier()
+    with TIMER.stage("rotate_forward+adam", device):
+        _, u_view, u_source = e.packed_segment("update", global_shape)
+        x_panel = e.planes("x_panel", rows, e.rows_of(cols))   # X[:, my row class]; reused by the right Gram
+        dist_gather(shard_source, IDENTITY, e.row_map(), rows, e.rows_of(cols), planes=x_panel)
+        e.two_sided(shard_source, global_shape, left_plain, right_plain, gathered=x_panel, mode=k.EPI_ADAM,
+                    out=u_view[: max(1, lr), : max(1, lc)],
+                    momentum=state["momentum"][: max(1, lr), : max(1, lc)],
+                    variance=state["variance"][: max(1, lr), : max(1, lc)], adam=adam)
+        e.comm.barrier()
     # backward rotation, result -> segment, then every rank pulls its tensor-parallel shard
-    _, o_view, o_source = e.packed_segment("output", global_shape)
-    e.two_sided(u_source, global_shape, left_t, right_t, mode=k.EPI_STORE, out=o_view[: max(1, lr), : max(1, lc)])
-    e.comm.barrier()
-    update = _pull_shard(e, o_source, global_shape, shard_dim)
+    with TIMER.stage("rotate_backward", device):
+        _, o_view, o_source = e.packed_segment("output", global_shape)
+        e.two_sided(u_source, global_shape, left_t, right_t, mode=k.EPI_STORE, out=o_view[: max(1, lr), : max(1, lc)])
+        e.comm.barrier()
+        update = _pull_shard(e, o_source, global_shape, shard_dim)
     # Gram EMAs with the current gradient; the right Gram reuses the gathered panel X[:, my row class]
-    _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
-    _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right", gathered=x_panel)
-    e.comm.barrier()
+    with TIMER.stage("gram", device):
+        _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
+        _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right", gathered=x_panel)
+        e.comm.barrier()
     if step % interval == 0:
-        refresh(e, state, global_shape)
+        with TIMER.stage("refresh", device):
+            refresh(e, state, global_shape)
     state["step"] = step
     return update
+
+
+def prepare_refresh(e: GridEngine, global_shape) -> None:
+    """Create (collectively) the segments and workspaces a refresh needs, so that the first refresh does
+    not pay for allocations and IPC handle exchanges in the middle of training."""
+    from . import qr as qr_driver
+
+    rows, cols = global_shape
+    for index, size in enumerate((rows, cols)):
+        e.packed_segment(f"factor_in{index}", (size, size))
+        e.comm.segment(f"factor_out{index}:{size}", size * size)
+        e.packed_segment("stage", (size, size))
+        e.packed_segment("basis", (size, size))
+        e.comm.segment(f"estimates:{size}:{e.nb}", max(1, numroc(size, e.nb, 0, e.Pc)))
+        if e.rank == _leader_of(index, 2, e.world):
+            qr_driver._workspace(size, e.device)
+    e.packed_segment("stage", global_shape)
+    e.packed_segment("middle", (cols, rows))
 
 
 def refresh(e: GridEngine, state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tensor]:
     rows, cols = global_shape
     grid, nb = e.grid, e.nb
-    rotate(state["momentum"], state["left_basis"], state["right_basis"], global_shape, nb, grid, "backward")
-    left_order = power_iteration_qr(state["left_preconditioner"], state["left_basis"], state["left_work"], rows, nb, grid)
-    right_order = power_iteration_qr(state["right_preconditioner"], state["right_basis"], state["right_work"], cols, nb, grid)
-    permute(state["variance"], global_shape, left_order, right_order, nb, grid)
-    rotate(state["momentum"], state["left_basis"], state["right_basis"], global_shape, nb, grid, "forward")
+    device = e.device
+    with TIMER.stage("refresh.momentum_out", device):
+        rotate(state["momentum"], state["left_basis"], state["right_basis"], global_shape, nb, grid, "backward")
+    with TIMER.stage("refresh.power_iteration", device):
+        left_order = estimated_order(state["left_preconditioner"], state["left_basis"], state["left_work"], rows, nb, grid)
+        right_order = estimated_order(state["right_preconditioner"], state["right_basis"], state["right_work"], cols, nb, grid)
+    with TIMER.stage("refresh.qr", device):
+        # the two factorisations are independent: they run at the same time on two different ranks
+        qr_many(e, [(state["left_work"], state["left_basis"], rows, left_order),
+                    (state["right_work"], state["right_basis"], cols, right_order)])
+
+    with TIMER.stage("refresh.permute_variance", device):
+        permute(state["variance"], global_shape, left_order, right_order, nb, grid)
+    with TIMER.stage("refresh.momentum_in", device):
+        rotate(state["momentum"], state["left_basis"], state["right_basis"], global_shape, nb, grid, "forward")
     return left_order, right_order

@@ -23,6 +23,7 @@ from typing import Any, Dict, MutableMapping, Optional, Tuple
 import torch
 from torch import Tensor
 
+from ..profiling import GLOBAL_STAGE_TIMER as TIMER
 from . import kernels as k
 from . import factor
 
@@ -134,7 +135,8 @@ def soap_step(
 ) -> Tensor:
     rows, cols = global_shape
     device = gradient.device
-    xp, gtp = _gradient_planes(gradient.reshape(rows, cols), rows, cols)
+    with TIMER.stage("split_gradient", device):
+        xp, gtp = _gradient_planes(gradient.reshape(rows, cols), rows, cols)
     if initializing:
         gram_updates(xp, gtp, state, beta, rows, cols)
         for side, size in (("left", rows), ("right", cols)):
@@ -143,6 +145,7 @@ def soap_step(
                 state[f"{side}_preconditioner"][:size, :size], state[f"{side}_basis"][:size, :size],
                 state[f"{side}_work"][:size, :size], values, implementation,
             )
+        prepare_refresh(rows, cols, device)
         state["step"] = 0
         return torch.zeros((rows, cols), dtype=torch.float32, device=device)
 
@@ -154,17 +157,35 @@ def soap_step(
     adam = dict(beta1=beta1, beta2=beta2, eps=eps / math.sqrt(bias2),
                 bias_correction1=1.0 - beta1**step, bias_correction2=bias2)
     up = workspace_planes("U", rows, cols, device)
-    rotate_planes(xp, ctx.left.plain, ctx.right.plain, rows, cols, device, tag="T",
-                  mode=k.EPI_ADAM, out_planes=up, momentum=state["momentum"][:rows, :cols],
-                  variance=state["variance"][:rows, :cols], adam=adam)
+    with TIMER.stage("rotate_forward+adam", device):
+        rotate_planes(xp, ctx.left.plain, ctx.right.plain, rows, cols, device, tag="T",
+                      mode=k.EPI_ADAM, out_planes=up, momentum=state["momentum"][:rows, :cols],
+                      variance=state["variance"][:rows, :cols], adam=adam)
     update = torch.empty((rows, cols), dtype=torch.float32, device=device)
-    rotate_planes(up, ctx.left.transposed, ctx.right.transposed, rows, cols, device, tag="T",
-                  mode=k.EPI_ROW_MAJOR, out=update)
-    gram_updates(xp, gtp, state, beta, rows, cols)
+    with TIMER.stage("rotate_backward", device):
+        rotate_planes(up, ctx.left.transposed, ctx.right.transposed, rows, cols, device, tag="T",
+                      mode=k.EPI_ROW_MAJOR, out=update)
+    with TIMER.stage("gram", device):
+        gram_updates(xp, gtp, state, beta, rows, cols)
     if step % interval == 0:
-        refresh(state, global_shape)
+        with TIMER.stage("refresh", device):
+            refresh(state, global_shape)
     state["step"] = step
     return update
+
+
+def prepare_refresh(rows: int, cols: int, device) -> None:
+    """Allocate what a refresh needs at initialisation time, so that the first refresh in the middle of
+    training launches kernels only."""
+    from . import qr as qr_driver
+
+    for size in {rows, cols}:
+        workspace_planes("P", size, size, device)
+        workspace_planes("Qtmp", size, size, device)
+        qr_driver._workspace(size, device)
+    workspace_matrix("perm", rows, cols, device)
+    for tag, depth, width in (("X", rows, cols), ("U", rows, cols), ("T", cols, rows)):
+        workspace_planes(tag, depth, width, device)
 
 
 def rotate(matrix: Tensor, Q_left: Tensor, Q_right: Tensor, global_shape, direction: str) -> Tensor:
@@ -216,15 +237,22 @@ def refresh(state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tens
     ctx.left.refresh(state["left_basis"], rows)
     ctx.right.refresh(state["right_basis"], cols)
     # momentum out of the old bases: Q_L M Q_R^T, kept as planes for the way back
-    mp = k.split_planes(momentum[:rows, :cols], out=workspace_planes("X", rows, cols, device))
-    parameter_space = workspace_planes("U", rows, cols, device)
-    rotate_planes(mp, ctx.left.transposed, ctx.right.transposed, rows, cols, device, tag="T",
-                  mode=k.EPI_SPLIT, out_planes=parameter_space)
-    left_order = power_iteration_qr(state["left_preconditioner"], state["left_basis"], state["left_work"], rows)
-    right_order = power_iteration_qr(state["right_preconditioner"], state["right_basis"], state["right_work"], cols)
-    permute(variance, global_shape, left_order, right_order)
-    ctx.left.refresh(state["left_basis"], rows)
-    ctx.right.refresh(state["right_basis"], cols)
-    rotate_planes(parameter_space, ctx.left.plain, ctx.right.plain, rows, cols, device, tag="T",
-                  mode=k.EPI_STORE, out=momentum[:rows, :cols])
+    with TIMER.stage("refresh.momentum_out", device):
+        mp = k.split_planes(momentum[:rows, :cols], out=workspace_planes("X", rows, cols, device))
+        parameter_space = workspace_planes("U", rows, cols, device)
+        rotate_planes(mp, ctx.left.transposed, ctx.right.transposed, rows, cols, device, tag="T",
+                      mode=k.EPI_SPLIT, out_planes=parameter_space)
+    with TIMER.stage("refresh.power_iteration", device):
+        left_order = estimated_order(state["left_preconditioner"], state["left_basis"], state["left_work"], rows)
+        right_order = estimated_order(state["right_preconditioner"], state["right_basis"], state["right_work"], cols)
+    with TIMER.stage("refresh.qr", device):
+        factor.householder_qr(state["left_work"][:rows, :rows], state["left_basis"][:rows, :rows], column_order=left_order)
+        factor.householder_qr(state["right_work"][:cols, :cols], state["right_basis"][:cols, :cols], column_order=right_order)
+    with TIMER.stage("refresh.permute_variance", device):
+        permute(variance, global_shape, left_order, right_order)
+    with TIMER.stage("refresh.momentum_in", device):
+        ctx.left.refresh(state["left_basis"], rows)
+        ctx.right.refresh(state["right_basis"], cols)
+        rotate_planes(parameter_space, ctx.left.plain, ctx.right.plain, rows, cols, device, tag="T",
+                      mode=k.EPI_STORE, out=momentum[:rows, :cols])
     return left_order, right_order
