@@ -12,6 +12,7 @@
 #include "comm.h"
 #include "elementwise.h"
 #include "gemm.h"
+#include "jacobi.h"
 #include "qr.h"
 
 namespace py = pybind11;
@@ -36,9 +37,12 @@ PYBIND11_MODULE(_C, m) {
          int mode, int symmetric, int force_narrow, float alpha, float beta, uint64_t C, int64_t ldc, uint64_t Chi,
          uint64_t Clo, int64_t ldp, uint64_t mom, uint64_t var, int64_t ldm, int64_t ldv, float beta1, float beta2,
          float eps, float inv_bc1, float inv_sqrt_bc2, int k_splits, int64_t split_stride, uint64_t status,
-         uint64_t stream) {
-        GemmOperands ops{ptr<const float>(a_hi), ptr<const float>(a_lo), lda,
-                         ptr<const float>(b_hi), ptr<const float>(b_lo), ldb};
+         uint64_t stream, int batches, int a_k_step, int a_row_step, int b_k_step, int b_row_step,
+         int64_t c_batch_stride, int64_t a_k_total, int64_t a_rows_total, int64_t b_k_total, int64_t b_rows_total,
+         uint64_t remap, uint64_t C2hi, uint64_t C2lo, int64_t ld2, int m_limit, int o1_row_start) {
+        GemmOperands ops{};
+        ops.a_hi = ptr<const float>(a_hi); ops.a_lo = ptr<const float>(a_lo); ops.lda = lda;
+        ops.b_hi = ptr<const float>(b_hi); ops.b_lo = ptr<const float>(b_lo); ops.ldb = ldb;
         GemmProblem prob{};
         prob.M = M; prob.N = N; prob.K = K;
         prob.mode = mode; prob.symmetric = symmetric; prob.force_narrow = force_narrow;
@@ -49,9 +53,24 @@ PYBIND11_MODULE(_C, m) {
         prob.beta1 = beta1; prob.beta2 = beta2; prob.eps = eps;
         prob.inv_bc1 = inv_bc1; prob.inv_sqrt_bc2 = inv_sqrt_bc2;
         prob.k_splits = k_splits; prob.split_stride = split_stride;
+        prob.batches = batches;
+        prob.a_k_step = a_k_step; prob.a_row_step = a_row_step; prob.b_k_step = b_k_step; prob.b_row_step = b_row_step;
+        prob.c_batch_stride = c_batch_stride;
+        ops.a_k_total = a_k_total; ops.a_rows_total = a_rows_total; ops.b_k_total = b_k_total; ops.b_rows_total = b_rows_total;
+        prob.remap = ptr<const int>(remap); prob.C2hi = ptr<float>(C2hi); prob.C2lo = ptr<float>(C2lo);
+        prob.ld2 = ld2; prob.m_limit = m_limit; prob.o1_row_start = o1_row_start;
         py::gil_scoped_release release;
         gemm_tf32x3(ops, prob, ptr<int>(status), stream_of(stream));
       },
+      py::arg("a_hi"), py::arg("a_lo"), py::arg("lda"), py::arg("b_hi"), py::arg("b_lo"), py::arg("ldb"), py::arg("M"),
+      py::arg("N"), py::arg("K"), py::arg("mode"), py::arg("symmetric"), py::arg("force_narrow"), py::arg("alpha"),
+      py::arg("beta"), py::arg("C"), py::arg("ldc"), py::arg("Chi"), py::arg("Clo"), py::arg("ldp"), py::arg("mom"),
+      py::arg("var"), py::arg("ldm"), py::arg("ldv"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"),
+      py::arg("inv_bc1"), py::arg("inv_sqrt_bc2"), py::arg("k_splits"), py::arg("split_stride"), py::arg("status"),
+      py::arg("stream"), py::arg("batches") = 1, py::arg("a_k_step") = 0, py::arg("a_row_step") = 0,
+      py::arg("b_k_step") = 0, py::arg("b_row_step") = 0, py::arg("c_batch_stride") = 0, py::arg("a_k_total") = 0,
+      py::arg("a_rows_total") = 0, py::arg("b_k_total") = 0, py::arg("b_rows_total") = 0, py::arg("remap") = 0,
+      py::arg("C2hi") = 0, py::arg("C2lo") = 0, py::arg("ld2") = 0, py::arg("m_limit") = 0, py::arg("o1_row_start") = 0,
       "3xTF32 tcgen05 GEMM acc[m,n] = sum_k Za[k,m] Zb[k,n] with fused epilogue");
 
   m.def("gemm_simt",
@@ -88,6 +107,12 @@ PYBIND11_MODULE(_C, m) {
                    ptr<const int64_t>(col_map), rows, cols, stream_of(stream));
         });
 
+  m.def("jacobi_small",
+        [](uint64_t s_hi, uint64_t s_lo, int64_t lds, int batches, uint64_t u_hi, uint64_t u_lo, int64_t ldu,
+           uint64_t offdiag, float scale, int max_sweeps, float tolerance, uint64_t stream) {
+          jacobi_small(ptr<const float>(s_hi), ptr<const float>(s_lo), lds, batches, ptr<float>(u_hi), ptr<float>(u_lo), ldu,
+                       ptr<float>(offdiag), scale, max_sweeps, tolerance, stream_of(stream));
+        });
   m.def("qr_panel",
         [](uint64_t p_hi, uint64_t p_lo, int64_t ldp, int r, int b, uint64_t v_hi, uint64_t v_lo, int64_t ldv,
            uint64_t vt_hi, uint64_t vt_lo, int64_t ldvt, uint64_t tau, uint64_t t_hi, uint64_t t_lo, uint64_t tt_hi,

@@ -10,6 +10,8 @@ enum EpilogueMode : int {
   kEpiSplit = 1,     // planes <- alpha*acc + beta*(old planes), as hi/lo (operand of the next GEMM); optional plain copy in C
   kEpiAdam = 2,      // acc is the projected gradient: update momentum/variance; update -> planes and/or C
   kEpiRowMajor = 3,  // C[m*ldc + n] = alpha*acc (tensor-parallel shard output)
+  kEpiPairUpdate = 4,  // block-Jacobi column-pair update: the 128 result columns of a batch item go, in two
+                       // halves of 64, to new column positions; written as planes in both orientations
 };
 
 // Operand planes.  a_* is the K x M column-major matrix Za (pitch lda floats), b_* the K x N matrix Zb.
@@ -20,6 +22,9 @@ struct GemmOperands {
   const float* b_hi;
   const float* b_lo;
   int64_t ldb;
+  // Extents of the whole operand buffers when a launch addresses sub-blocks of them per batch item
+  // (0: the operand is exactly K x M, resp. K x N).
+  int64_t a_k_total = 0, a_rows_total = 0, b_k_total = 0, b_rows_total = 0;
 };
 
 struct GemmProblem {
@@ -39,6 +44,17 @@ struct GemmProblem {
   float* var;
   int64_t ldm, ldv;
   float beta1, beta2, eps, inv_bc1, inv_sqrt_bc2;
+  // Batching (blockIdx.z = batch item): operand sub-blocks start at these multiples of the item index.
+  int batches;
+  int a_k_step, a_row_step, b_k_step, b_row_step;
+  int64_t c_batch_stride;      // kEpiStore: item b writes at C + b * c_batch_stride
+  // kEpiPairUpdate
+  const int* remap;            // [batches][2]: destination position (in units of 64 columns) of each half
+  float* C2hi;                 // second orientation: element (m, c') at [m + c' * ld2], only rows m < m_limit
+  float* C2lo;
+  int64_t ld2;
+  int m_limit;
+  int o1_row_start;            // rows m < o1_row_start are not written in the first orientation
 };
 
 // acc[m, n] = sum_k Za[k, m] * Zb[k, n] on tcgen05 with 3xTF32 compensation, then the epilogue.

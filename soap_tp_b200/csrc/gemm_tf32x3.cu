@@ -253,6 +253,47 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
   }
 }
 
+// Block-Jacobi pair update (N = 128): result column n' of batch item b becomes column
+// c' = 64 * remap[2b + (n' >= 64)] + (n' & 63) of the next arrangement.  The result is written as
+// operand planes in two orientations: (m, c') at [c' + m * ldp] (the operand of the next pair update)
+// and, for rows m < m_limit, at [m + c' * ld2] (the operand of the next Gram product).
+template <int BN>
+__device__ __forceinline__ void run_pair_update(const GemmProblem& prob, const float* tile, int m0, int ew, int lane,
+                                                int batch) {
+  const int pos0 = prob.remap[2 * batch], pos1 = prob.remap[2 * batch + 1];
+  const int rows = min(kBM, prob.M - m0);
+  // orientation 1: one warp per result row, lanes along the result columns (runs of 32 contiguous floats)
+  for (int r = ew; r < rows; r += kEpiWarps) {
+    if (m0 + r < prob.o1_row_start) continue;
+    const int64_t row_base = static_cast<int64_t>(m0 + r) * prob.ldp;
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      const int nl = part * 32 + lane;
+      const int dst = ((nl < 64) ? pos0 : pos1) * 64 + (nl & 63);
+      const float v = tile[nl * kTilePitch + r];
+      const float hi = tf32_round(v);
+      prob.Chi[row_base + dst] = hi;
+      prob.Clo[row_base + dst] = v - hi;
+    }
+  }
+  // orientation 2: one warp per result column, four rows per lane
+  if (prob.C2hi != nullptr && m0 < prob.m_limit && rows == kBM) {
+    for (int nl = ew; nl < 128; nl += kEpiWarps) {
+      const int dst = ((nl < 64) ? pos0 : pos1) * 64 + (nl & 63);
+      const Vec4 v = load4(tile + nl * kTilePitch + 4 * lane);
+      Vec4 hi, lo;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        hi.v[i] = tf32_round(v.v[i]);
+        lo.v[i] = v.v[i] - hi.v[i];
+      }
+      const int64_t off = (m0 + 4 * lane) + static_cast<int64_t>(dst) * prob.ld2;
+      store4(prob.C2hi + off, hi);
+      store4(prob.C2lo + off, lo);
+    }
+  }
+}
+
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmProblem prob, int* status) {
@@ -332,10 +373,13 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
       uint8_t* stage = smem + s * Cfg::kStageBytes;
       mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
       const int k0 = (kb_first + kb) * kBK;
-      tma_load_2d(stage, &maps.a_hi, &full_bar[s], k0, m0);
-      tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], k0, m0);
-      tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], k0, n0);
-      tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], k0, n0);
+      const int batch = blockIdx.z;
+      const int ka = k0 + batch * prob.a_k_step, kbb = k0 + batch * prob.b_k_step;
+      const int ra = m0 + batch * prob.a_row_step, rb = n0 + batch * prob.b_row_step;
+      tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
+      tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka, ra);
+      tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], kbb, rb);
+      tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb, rb);
     }
     if (*abort_flag) {
       // give copies that are still in flight time to land before the CTA's shared memory is released
@@ -421,8 +465,10 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
     }
     asm volatile("bar.sync 1, %0;" ::"r"(kEpiWarps * 32) : "memory");
     if (ok) {
-      const int64_t c_shift = (gridDim.y > 1) ? static_cast<int64_t>(blockIdx.y) * prob.split_stride : 0;
-      run_epilogue<BN, MODE>(prob, tile, m0, n0, ew, lane, c_shift);
+      const int64_t c_shift = ((gridDim.y > 1) ? static_cast<int64_t>(blockIdx.y) * prob.split_stride : 0) +
+                              static_cast<int64_t>(blockIdx.z) * prob.c_batch_stride;
+      if constexpr (MODE == kEpiPairUpdate) run_pair_update<BN>(prob, tile, m0, ew, lane, blockIdx.z);
+      else run_epilogue<BN, MODE>(prob, tile, m0, n0, ew, lane, c_shift);
     }
   }
 
@@ -482,14 +528,16 @@ void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaS
     configured = true;
   }
   GemmMaps maps;
-  maps.a_hi = make_operand_map(ops.a_hi, prob.K, prob.M, ops.lda, kBM);
-  maps.a_lo = make_operand_map(ops.a_lo, prob.K, prob.M, ops.lda, kBM);
-  maps.b_hi = make_operand_map(ops.b_hi, prob.K, prob.N, ops.ldb, BN);
-  maps.b_lo = make_operand_map(ops.b_lo, prob.K, prob.N, ops.ldb, BN);
+  const int64_t a_k = ops.a_k_total ? ops.a_k_total : prob.K, a_rows = ops.a_rows_total ? ops.a_rows_total : prob.M;
+  const int64_t b_k = ops.b_k_total ? ops.b_k_total : prob.K, b_rows = ops.b_rows_total ? ops.b_rows_total : prob.N;
+  maps.a_hi = make_operand_map(ops.a_hi, a_k, a_rows, ops.lda, kBM);
+  maps.a_lo = make_operand_map(ops.a_lo, a_k, a_rows, ops.lda, kBM);
+  maps.b_hi = make_operand_map(ops.b_hi, b_k, b_rows, ops.ldb, BN);
+  maps.b_lo = make_operand_map(ops.b_lo, b_k, b_rows, ops.ldb, BN);
   const int tiles_m = (prob.M + kBM - 1) / kBM;
   const int tiles_n = (prob.N + BN - 1) / BN;
   const int splits = (MODE == kEpiStore && prob.k_splits > 1) ? prob.k_splits : 1;
-  dim3 grid(tiles_m * tiles_n, splits);
+  dim3 grid(tiles_m * tiles_n, splits, prob.batches > 1 ? prob.batches : 1);
   gemm_tf32x3_kernel<BN, MODE><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(maps, prob, status);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) throw std::runtime_error(std::string("gemm_tf32x3 launch: ") + cudaGetErrorString(err));
@@ -515,6 +563,11 @@ void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, 
       break;
     case kEpiRowMajor:
       wide ? launch<256, kEpiRowMajor>(ops, prob, status, stream) : launch<128, kEpiRowMajor>(ops, prob, status, stream);
+      break;
+    case kEpiPairUpdate:
+      if (prob.N != 128 || prob.remap == nullptr || prob.Chi == nullptr)
+        throw std::invalid_argument("gemm_tf32x3: the pair update needs N = 128, a remap table and output planes");
+      launch<128, kEpiPairUpdate>(ops, prob, status, stream);
       break;
     default:
       throw std::invalid_argument("gemm_tf32x3: unknown epilogue mode");

@@ -593,6 +593,9 @@ def prepare_refresh(e: GridEngine, global_shape) -> None:
             qr_driver._workspace(size, e.device)
     e.packed_segment("stage", global_shape)
     e.packed_segment("middle", (cols, rows))
+    from . import local
+
+    local.warm_refresh_kernels(e.device)
 
 
 def refresh(e: GridEngine, state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tensor]:

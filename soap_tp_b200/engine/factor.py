@@ -22,6 +22,16 @@ def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = N
     return qr.householder_qr(matrix, Q, column_order)
 
 
+def householder_qr_pair(jobs) -> None:
+    """Several independent QR factorisations issued concurrently; ``jobs``: ``(matrix, Q, column_order)``."""
+    from ..ops.basis import count_qr_call
+    from . import qr
+
+    for _ in jobs:
+        count_qr_call()
+    qr.householder_qr_pair(jobs)
+
+
 def symmetric_eigenbasis(P: Tensor, Q: Tensor, work: Tensor, values: Tensor, implementation: str) -> Tensor:
     """Eigenvectors of symmetric ``P`` into ``Q`` and eigenvalues into ``values``, both descending."""
     from . import jacobi

@@ -23,7 +23,7 @@ except ImportError:  # pragma: no cover - build on first use
     build_ext.build()
     from .. import _C  # type: ignore[attr-defined]
 
-EPI_STORE, EPI_SPLIT, EPI_ADAM, EPI_ROW_MAJOR = 0, 1, 2, 3
+EPI_STORE, EPI_SPLIT, EPI_ADAM, EPI_ROW_MAJOR, EPI_PAIR_UPDATE = 0, 1, 2, 3, 4
 
 STATUS_MESSAGES = {
     1: "GEMM consumer timed out waiting for a TMA stage",
@@ -154,14 +154,18 @@ def gemm(
     force_narrow: bool = False,
     k_splits: int = 1,
     split_stride: int = 0,
+    batch: Optional[dict] = None,
 ) -> None:
     """``acc[m, n] = sum_k a[k, m] * b[k, n]`` then the fused epilogue (see ``csrc/gemm.h``).
 
     ``out`` is a column-major ``M x N`` view for ``EPI_STORE`` (and the optional plain copy of
     ``EPI_SPLIT``/``EPI_ADAM``) or a row-major ``M x N`` tensor for ``EPI_ROW_MAJOR``.
     """
-    assert a.depth == b.depth, (a.depth, b.depth)
-    M, N, K = a.cols, b.cols, a.depth
+    if batch is None:
+        assert a.depth == b.depth, (a.depth, b.depth)
+        M, N, K = a.cols, b.cols, a.depth
+    else:
+        M, N, K = batch["M"], batch["N"], batch["K"]   # per batch item; a and b describe the whole buffers
     if M == 0 or N == 0:
         return
     c_ptr, ldc = 0, 0
@@ -175,7 +179,7 @@ def gemm(
             ldc = out_ld if out_ld is not None else (out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0]))
     chi = clo = ldp = 0
     if out_planes is not None:
-        assert out_planes.depth == M and out_planes.cols == N
+        assert batch is not None or (out_planes.depth == M and out_planes.cols == N)
         chi, clo, ldp = out_planes.hi.data_ptr(), out_planes.lo.data_ptr(), out_planes.ld
     mom = var = ldm = ldv = 0
     b1 = b2 = eps = ibc1 = isbc2 = 0.0
@@ -190,9 +194,26 @@ def gemm(
     _C.gemm_tf32x3(a.hi.data_ptr(), a.lo.data_ptr(), a.ld, b.hi.data_ptr(), b.lo.data_ptr(), b.ld, M, N, K,
                    mode, int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
                    mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, int(k_splits), int(split_stride), status.data_ptr(),
-                   _stream())
+                   _stream(), **_batch_arguments(a, b, batch))
     mark_written(out, momentum, variance)
     _count("gemm_tf32x3_kernel")
+
+
+def _batch_arguments(a: "Planes", b: "Planes", batch: Optional[dict]) -> dict:
+    """Keyword arguments of the batched launch (see ``csrc/gemm.h``): ``a`` and ``b`` are the whole operand
+    buffers, the per-item sub-blocks start at multiples of the ``*_step`` values."""
+    if batch is None:
+        return {}
+    second = batch.get("out2_planes")
+    remap = batch.get("remap")
+    return dict(
+        batches=int(batch["count"]), a_k_step=int(batch.get("a_k_step", 0)), a_row_step=int(batch.get("a_row_step", 0)),
+        b_k_step=int(batch.get("b_k_step", 0)), b_row_step=int(batch.get("b_row_step", 0)),
+        c_batch_stride=int(batch.get("c_batch_stride", 0)), a_k_total=a.depth, a_rows_total=a.cols, b_k_total=b.depth,
+        b_rows_total=b.cols, remap=remap.data_ptr() if remap is not None else 0,
+        C2hi=second.hi.data_ptr() if second is not None else 0, C2lo=second.lo.data_ptr() if second is not None else 0,
+        ld2=second.ld if second is not None else 0, m_limit=int(batch.get("m_limit", 0)),
+        o1_row_start=int(batch.get("o1_row_start", 0)))
 
 
 def gemm_simt(a: Tensor, b: Tensor, out: Tensor, *, alpha: float = 1.0, beta: float = 0.0) -> Tensor:

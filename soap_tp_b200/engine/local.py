@@ -17,6 +17,7 @@ basis tensor changes (refresh, initialisation, or a user writing into ``state``)
 from __future__ import annotations
 
 import math
+import os
 from collections import OrderedDict
 from typing import Any, Dict, MutableMapping, Optional, Tuple
 
@@ -174,6 +175,33 @@ def soap_step(
     return update
 
 
+_WARMED: Dict[str, bool] = {}
+
+
+def warm_refresh_kernels(device) -> None:
+    """Launch every kernel variant a refresh uses once, on a tiny problem.
+
+    CUDA loads a kernel's code the first time it is launched; without this the first refresh of a
+    training run pays tens of milliseconds of module loading in the middle of a step.
+    """
+    key = str(torch.device(device))
+    if _WARMED.get(key):
+        return
+    _WARMED[key] = True
+    n = 384
+    generator = torch.Generator(device=device).manual_seed(0)
+    matrix = torch.randn(n, n, generator=generator, device=device).T
+    out = torch.empty(n, n, device=device).T
+    order = torch.randperm(n, generator=generator, device=device)
+    factor_jobs = [(matrix.clone(), out, order), (matrix.clone(), torch.empty(n, n, device=device).T, None)]
+    from . import qr as qr_driver
+
+    qr_driver.householder_qr_pair(factor_jobs)
+    estimated_order(matrix, out, torch.empty(n, n, device=device).T, n)
+    k.gather2d(matrix, out, order, order)
+    qr_driver.release_workspaces_for(n, device)
+
+
 def prepare_refresh(rows: int, cols: int, device) -> None:
     """Allocate what a refresh needs at initialisation time, so that the first refresh in the middle of
     training launches kernels only."""
@@ -182,10 +210,15 @@ def prepare_refresh(rows: int, cols: int, device) -> None:
     for size in {rows, cols}:
         workspace_planes("P", size, size, device)
         workspace_planes("Qtmp", size, size, device)
-        qr_driver._workspace(size, device)
+        qr_driver._workspace(size, device, 0)
+    if rows == cols:
+        qr_driver._workspace(cols, device, 1)     # the second of two concurrent factorisations
+    else:
+        qr_driver._workspace(rows, device, 0), qr_driver._workspace(cols, device, 1)
     workspace_matrix("perm", rows, cols, device)
     for tag, depth, width in (("X", rows, cols), ("U", rows, cols), ("T", cols, rows)):
         workspace_planes(tag, depth, width, device)
+    warm_refresh_kernels(device)
 
 
 def rotate(matrix: Tensor, Q_left: Tensor, Q_right: Tensor, global_shape, direction: str) -> Tensor:
@@ -246,8 +279,14 @@ def refresh(state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tens
         left_order = estimated_order(state["left_preconditioner"], state["left_basis"], state["left_work"], rows)
         right_order = estimated_order(state["right_preconditioner"], state["right_basis"], state["right_work"], cols)
     with TIMER.stage("refresh.qr", device):
-        factor.householder_qr(state["left_work"][:rows, :rows], state["left_basis"][:rows, :rows], column_order=left_order)
-        factor.householder_qr(state["right_work"][:cols, :cols], state["right_basis"][:cols, :cols], column_order=right_order)
+        # the two factorisations are independent: issued on two streams they fill each other's gaps
+        if os.environ.get("SOAP_TP_SERIAL_QR", "0") == "1":
+            factor.householder_qr(state["left_work"][:rows, :rows], state["left_basis"][:rows, :rows], column_order=left_order)
+            factor.householder_qr(state["right_work"][:cols, :cols], state["right_basis"][:cols, :cols], column_order=right_order)
+        else:
+            factor.householder_qr_pair([
+                (state["left_work"][:rows, :rows], state["left_basis"][:rows, :rows], left_order),
+                (state["right_work"][:cols, :cols], state["right_basis"][:cols, :cols], right_order)])
     with TIMER.stage("refresh.permute_variance", device):
         permute(variance, global_shape, left_order, right_order)
     with TIMER.stage("refresh.momentum_in", device):

@@ -27,8 +27,8 @@ PANEL = _C.QR_PANEL_WIDTH
 _WORKSPACES: Dict[tuple, dict] = {}
 
 
-def _workspace(n: int, device) -> dict:
-    key = (n, str(device))
+def _workspace(n: int, device, slot: int = 0) -> dict:
+    key = (n, str(device), slot)
     ws = _WORKSPACES.get(key)
     if ws is None:
         panels = -(-n // PANEL)
@@ -55,6 +55,11 @@ def release_workspaces() -> None:
     _WORKSPACES.clear()
 
 
+def release_workspaces_for(n: int, device) -> None:
+    for key in [key for key in _WORKSPACES if key[0] == n and key[1] == str(device)]:
+        del _WORKSPACES[key]
+
+
 def _splits(tiles: int, k_blocks: int) -> int:
     wanted = max(1, -(-296 // max(1, tiles)))
     return max(1, min(wanted, 16, max(1, k_blocks // 4)))
@@ -74,10 +79,59 @@ def _skinny_product(ws: dict, a: k.Planes, b: k.Planes, out: k.Planes) -> None:
 
 
 def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = None) -> Tensor:
+    """``Q <- explicit orthogonal factor of matrix[:, column_order]`` on the current stream."""
+    for _ in _factorisation_steps(matrix, Q, column_order, 0):
+        pass
+    return Q
+
+
+_SIDE_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
+
+
+def householder_qr_pair(jobs) -> None:
+    """Factor several independent matrices at the same time.
+
+    ``jobs`` is a list of ``(matrix, Q, column_order)``.  Each factorisation is issued panel by panel on
+    its own stream, alternating between the jobs, so that the latency-bound panel kernel of one
+    factorisation (a few dozen thread blocks) runs while the tensor-core updates of the other keep the
+    remaining SMs busy.  The calling stream waits for all of them.
+    """
+    if len(jobs) == 1:
+        householder_qr(*jobs[0])
+        return
+    device = jobs[0][0].device
+    main = torch.cuda.current_stream(device)
+    ready = torch.cuda.Event()
+    ready.record(main)
+    streams, steps = [], []
+    for slot, (matrix, Q, order) in enumerate(jobs):
+        key = (str(device), slot)
+        if key not in _SIDE_STREAMS:
+            _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+        stream = _SIDE_STREAMS[key]
+        stream.wait_event(ready)
+        streams.append(stream)
+        steps.append(_factorisation_steps(matrix, Q, order, slot))
+    alive = list(range(len(jobs)))
+    while alive:
+        for slot in list(alive):
+            with torch.cuda.stream(streams[slot]):
+                try:
+                    next(steps[slot])
+                except StopIteration:
+                    alive.remove(slot)
+    for stream in streams:
+        done = torch.cuda.Event()
+        done.record(stream)
+        main.wait_event(done)
+
+
+def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor], slot: int):
+    """The blocked factorisation as a generator: yields after the launches of every panel."""
     n = matrix.shape[0]
     assert matrix.shape == (n, n) and Q.shape == (n, n)
     device = matrix.device
-    ws = _workspace(n, device)
+    ws = _workspace(n, device, slot)
     C, Qp, V = ws["C"], ws["Q"], ws["V"]
     source = matrix
     if column_order is not None:
@@ -106,6 +160,7 @@ def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = N
             trailing = C.sub(j0, j0 + bw, r, nc)
             _skinny_product(ws, v, trailing, w)                                             # W = V^T C
             k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=trailing, alpha=-1.0, beta=1.0)        # C -= Z^T W
+        yield
     # explicit Q = H_0 H_1 ... applied to the identity, last panel first
     _C.identity_planes(Qp.hi.data_ptr(), Qp.lo.data_ptr(), Qp.ld, n, n, stream())
     k._count("identity_planes_kernel")
@@ -122,5 +177,5 @@ def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = N
         _skinny_product(ws, v, block, w)                                                    # W = V^T Q
         k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0,
                out=Q if p == 0 else None)                                                   # Q -= Z^T W
+        yield
     k.mark_written(Q)
-    return Q
