@@ -13,7 +13,9 @@ from distributed_helpers import run_distributed
 pytestmark = pytest.mark.gpu
 
 RECT = [(8, 8), (8, 12), (12, 8), (9, 13), (13, 9)]
-TINY = (10, 2, (0.8, 0.9), 0.75, 1e-6, 1e-5, "eigh", 2.0, 1e-6)   # ..., noise-floor perturbation
+# ..., noise-floor perturbation: 3e-6 relative is the measured backward error of the device eigensolver and
+# of a chain of 3xTF32 products (residual ||P Q - Q diag|| / ||P|| = 1e-6 ... 2.5e-6 for n = 1024 ... 8192)
+TINY = (10, 2, (0.8, 0.9), 0.75, 1e-6, 1e-5, "eigh", 2.0, 3e-6)
 
 
 def test_single_gpu_ops():
