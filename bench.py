@@ -237,13 +237,34 @@ def run(args: argparse.Namespace) -> int:
     host_pool = [torch.empty(shard_shape, dtype=torch.float32).pin_memory() for _ in range(pool)]
     for i, buffer in enumerate(host_pool):
         buffer.copy_(gradient_for(counter + i, rank, shard_shape, device, cache))
-    device_buffer = torch.empty(shard_shape, dtype=torch.float32, device=device)
+    # Every step's input crosses PCIe inside the timed region; the copy of step i + 1 is issued on a copy
+    # stream while step i computes (two device buffers), as an input pipeline would do it.
+    device_buffers = [torch.empty(shard_shape, dtype=torch.float32, device=device) for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=device)
+    arrived = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    used = [False, False]
     metric_host = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def prefetch(index: int) -> None:
+        slot = index % 2
+        with torch.cuda.stream(copy_stream):
+            if used[slot]:
+                copy_stream.wait_event(consumed[slot])
+            device_buffers[slot].copy_(host_pool[index % pool], non_blocking=True)
+            arrived[slot].record(copy_stream)
+
     fence()
     e2e_start = time.perf_counter()
+    prefetch(0)
     for i in range(args.steps):
-        device_buffer.copy_(host_pool[i % pool], non_blocking=True)
-        update = step_fn(device_buffer)
+        slot = i % 2
+        if i + 1 < args.steps:
+            prefetch(i + 1)
+        torch.cuda.current_stream().wait_event(arrived[slot])
+        update = step_fn(device_buffers[slot])
+        consumed[slot].record()
+        used[slot] = True
         metric_host.copy_(torch.linalg.vector_norm(update).reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()
     fence()

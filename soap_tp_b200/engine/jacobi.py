@@ -81,7 +81,7 @@ def release_workspaces() -> None:
 
 
 def symmetric_eigenbasis(P: Tensor, Q: Tensor, work: Tensor, values: Tensor, *, tolerance: float = 4e-6,
-                         max_sweeps: int = 16) -> Tensor:
+                         max_sweeps: int = 24) -> Tensor:
     n = P.shape[0]
     device = P.device
     size = -(-n // PAIR) * PAIR
@@ -110,12 +110,17 @@ def symmetric_eigenbasis(P: Tensor, Q: Tensor, work: Tensor, values: Tensor, *, 
     rows = dict(count=pairs, M=size, N=PAIR, K=PAIR, a_k_step=PAIR, b_row_step=PAIR, remap=remap)
     current = 0
     sweeps_done = 0
+    last_offdiag = 1.0
     for sweep in range(max_sweeps):
         ws["offdiag"].zero_()
+        # While the matrix is far from diagonal the diagonal blocks need not be diagonalised to working
+        # precision: a few inner sweeps give the same outer convergence at a fraction of the cost
+        # (a fully dense 128 x 128 block costs 0.4 ms per inner sweep, a converged one 0.2 ms in total).
+        inner_sweeps = 2 if (blocks > 2 and last_offdiag > 1e-3) else 10
         for _ in range(max(1, blocks - 1)):
             nxt = current ^ 1
             _C.jacobi_small(S[current].hi.data_ptr(), S[current].lo.data_ptr(), S[current].ld, pairs, U.hi.data_ptr(),
-                            U.lo.data_ptr(), U.ld, ws["offdiag"].data_ptr(), scale, 10, 1e-7, k._stream())
+                            U.lo.data_ptr(), U.ld, ws["offdiag"].data_ptr(), scale, inner_sweeps, 1e-7, k._stream())
             k._count("jacobi_small_kernel")
             # [M; V] J: the V part goes to the next arrangement, (M J)^T lands in R
             k.gemm(S[current], U, mode=k.EPI_PAIR_UPDATE, out_planes=S[nxt], force_narrow=True, batch=columns)
@@ -123,7 +128,8 @@ def symmetric_eigenbasis(P: Tensor, Q: Tensor, work: Tensor, values: Tensor, *, 
             k.gemm(R, U, mode=k.EPI_PAIR_UPDATE, out_planes=S[nxt], force_narrow=True, batch=rows)
             current = nxt
         sweeps_done = sweep + 1
-        if float(ws["offdiag"].item()) <= tolerance:
+        last_offdiag = float(ws["offdiag"].item())
+        if last_offdiag <= tolerance:
             break
     final = S[current].dense()                       # (K = column j) x (rows: M rows then V rows)
     eigen = final[:, :size].diagonal().clone()

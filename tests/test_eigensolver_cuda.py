@@ -28,4 +28,4 @@ def test_jacobi_matches_lapack(n, rank):
     assert float((vd - expected).abs().max()) <= 1e-5 * scale
     assert float((Qd.T @ Qd - torch.eye(n, dtype=torch.float64)).abs().max()) <= 2e-5
     assert float((P64 @ Qd - Qd * vd).abs().max()) <= 5e-5 * scale
-    assert jacobi.symmetric_eigenbasis.last_sweeps <= 14
+    assert jacobi.symmetric_eigenbasis.last_sweeps <= 20
