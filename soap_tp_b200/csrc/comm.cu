@@ -14,7 +14,9 @@
 //                       tensor-parallel row/column shards) and the maps are block-cyclic
 //                       local->global maps optionally composed with a permutation vector.  Output
 //                       is either a plain strided matrix or the hi/lo operand planes of the 3xTF32
-//                       GEMM (all-gather fused with the operand split).
+//                       GEMM (all-gather fused with the operand split).  With `upper_only` only
+//                       entries whose mapped row is above their mapped column are written (pull
+//                       of the mirrored half of a symmetric matrix).
 //   barrier_kernel      one flag per peer in each rank's signal pad, release store to every peer,
 //                       bounded acquire spin on the own pad.  Used only when every rank has its own
 //                       GPU; ranks that share a GPU order themselves on the host instead.
@@ -106,8 +108,8 @@ __device__ __forceinline__ float tf32_round_dev(float x) {
 // source(row = map_j(j), col = map_i(i)) : source(row = map_i(i), col = map_j(j)).
 // read_i_fast tells whether consecutive i touch consecutive source addresses (chosen by the host).
 __global__ void __launch_bounds__(256)
-dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, int read_i_fast, float* out_hi,
-                   float* out_lo, int64_t d_i, int64_t d_j, int rows_out, int cols_out) {
+dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, int read_i_fast, int upper_only,
+                   float* out_hi, float* out_lo, int64_t d_i, int64_t d_j, int rows_out, int cols_out) {
   __shared__ float tile[32][33];
   const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
   const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
@@ -117,14 +119,14 @@ dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose
     float val = 0.f;
     if (i < rows_out && j < cols_out) {
       const int a = map_index(map_i, i), b = map_index(map_j, j);
-      val = transpose ? load_source(src, b, a) : load_source(src, a, b);
+      if (!upper_only || a < b) val = transpose ? load_source(src, b, a) : load_source(src, a, b);
     }
     if (read_i_fast) tile[t][tx] = val; else tile[tx][t] = val;
   }
   __syncthreads();
   for (int t = ty; t < 32; t += 8) {
     const int i = i0 + tx, j = j0 + t;
-    if (i < rows_out && j < cols_out) {
+    if (i < rows_out && j < cols_out && (!upper_only || map_index(map_i, i) < map_index(map_j, j))) {
       const float x = tile[t][tx];
       const int64_t off = i * d_i + j * d_j;
       if (out_lo) {
@@ -192,7 +194,7 @@ void register_comm(py::module_& m) {
   m.def("dist_gather",
         [](uint64_t peers, int kind, int rows, int cols, int nb_r, int nb_c, int Pr, int Pc, int world, int ip, int iP,
            int inb, int ioff, uint64_t iperm, int jp, int jP, int jnb, int joff, uint64_t jperm, int transpose,
-           uint64_t out_hi, uint64_t out_lo,
+           int upper_only, uint64_t out_hi, uint64_t out_lo,
            int64_t d_i, int64_t d_j, int rows_out, int cols_out, uint64_t stream) {
           if (rows_out <= 0 || cols_out <= 0) return;
           DistSource src{reinterpret_cast<const float* const*>(peers), kind, rows, cols, nb_r, nb_c, Pr, Pc, world};
@@ -205,7 +207,7 @@ void register_comm(py::module_& m) {
           const int read_i_fast = (i_is_source_row == source_row_contiguous) ? 1 : 0;
           dim3 grid((rows_out + 31) / 32, (cols_out + 31) / 32);
           dist_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-              src, mi, mj, transpose, read_i_fast, reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), d_i,
+              src, mi, mj, transpose, read_i_fast, upper_only, reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), d_i,
               d_j, rows_out, cols_out);
           check(cudaGetLastError(), "dist_gather_kernel");
         });

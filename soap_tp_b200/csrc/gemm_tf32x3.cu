@@ -75,6 +75,17 @@ __device__ __forceinline__ float tf32_round(float x) {
   return __uint_as_float(r);
 }
 
+// Global row / column of a local index.  symmetric == 1: the operands are whole matrices, indices are
+// global already.  symmetric == 2: the output is this rank's packed block-cyclic part of a symmetric
+// matrix; only entries on or below the GLOBAL diagonal are produced (the rest is pulled from the
+// peers that own the mirrored entries).
+__device__ __forceinline__ int global_row(const GemmProblem& p, int m) {
+  return p.symmetric == 2 ? ((m / p.tri_nb) * p.tri_Pr + p.tri_pr) * p.tri_nb + m % p.tri_nb : m;
+}
+__device__ __forceinline__ int global_col(const GemmProblem& p, int n) {
+  return p.symmetric == 2 ? ((n / p.tri_nb) * p.tri_Pc + p.tri_pc) * p.tri_nb + n % p.tri_nb : n;
+}
+
 constexpr int kTilePitch = kBM + 4;   // floats between columns of the staged tile (keeps 16-byte alignment)
 
 struct Vec4 {
@@ -96,7 +107,7 @@ __device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t
     float v = prob.alpha * acc;
     if (prob.beta != 0.0f) v = fmaf(prob.beta, *dst, v);
     *dst = v;
-    if (prob.symmetric && n < m) prob.C[c_shift + n + static_cast<int64_t>(m) * prob.ldc] = v;
+    if (prob.symmetric == 1 && n < m) prob.C[c_shift + n + static_cast<int64_t>(m) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiSplit) {
     const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
     float v = prob.alpha * acc;
@@ -151,7 +162,7 @@ __device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t
       out.v[i] = v;
     }
     store4(prob.C + c_shift + m + static_cast<int64_t>(n) * prob.ldc, out);
-    if (prob.symmetric) {
+    if (prob.symmetric == 1) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         if (n < m + i) prob.C[c_shift + n + static_cast<int64_t>(m + i) * prob.ldc] = out.v[i];
@@ -209,7 +220,7 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
     }
     return;
   }
-  bool vector = rows == kBM;
+  bool vector = rows == kBM && !(prob.symmetric == 2 && (prob.tri_nb & 3) != 0);
   if constexpr (MODE == kEpiStore) vector = vector && aligned16(prob.C + c_shift, prob.ldc);
   if constexpr (MODE == kEpiSplit)
     vector = vector && aligned16(prob.Chi, prob.ldp) && aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);
@@ -221,7 +232,7 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
       const int n = n0 + nl;
       for (int r = lane; r < rows; r += 32) {
         const int m = m0 + r;
-        if (prob.symmetric && n > m) continue;
+        if (prob.symmetric && global_col(prob, n) > global_row(prob, m)) continue;
         epilogue_scalar<MODE>(prob, c_shift, m, n, tile[nl * kTilePitch + r]);
       }
     }
@@ -229,6 +240,7 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
   }
   constexpr int kUnroll = 4;   // columns per warp whose loads are in flight together
   const int m = m0 + 4 * lane;
+  const int gm = global_row(prob, m);   // the four rows of a lane are consecutive globally too (block sizes are multiples of 4)
   for (int base = ew * kUnroll; base < cols; base += kEpiWarps * kUnroll) {
     Vec4 old0[kUnroll], old1[kUnroll];
     int state[kUnroll];        // 0: skip, 1: vector, 2: element by element (diagonal band of a symmetric product)
@@ -236,7 +248,10 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
     for (int u = 0; u < kUnroll; ++u) {
       const int nl = base + u, n = n0 + nl;
       state[u] = (nl < cols) ? 1 : 0;
-      if (prob.symmetric && state[u]) state[u] = (n > m + 3) ? 0 : (n > m ? 2 : 1);
+      if (prob.symmetric && state[u]) {
+        const int gn = global_col(prob, n);
+        state[u] = (gn > gm + 3) ? 0 : (gn > gm ? 2 : 1);
+      }
       old0[u] = old1[u] = Vec4{{0.f, 0.f, 0.f, 0.f}};
       if (state[u] == 1) epilogue_load4<MODE>(prob, c_shift, m, n, old0[u], old1[u]);
     }
@@ -246,8 +261,9 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
       if (state[u] == 1) {
         epilogue_store4<MODE>(prob, c_shift, m, n, load4(tile + nl * kTilePitch + 4 * lane), old0[u], old1[u]);
       } else if (state[u] == 2) {
+        const int gn = global_col(prob, n);
         for (int i = 0; i < 4; ++i)
-          if (n <= m + i) epilogue_scalar<MODE>(prob, c_shift, m + i, n, tile[nl * kTilePitch + 4 * lane + i]);
+          if (gn <= gm + i) epilogue_scalar<MODE>(prob, c_shift, m + i, n, tile[nl * kTilePitch + 4 * lane + i]);
       }
     }
   }
@@ -327,7 +343,7 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
   const int m0 = tile_m * kBM;
   const int n0 = tile_n * BN;
   // Symmetric products: tiles strictly above the diagonal are produced by mirroring.
-  if (prob.symmetric && n0 > m0 + kBM - 1) return;
+  if (prob.symmetric && global_col(prob, n0) > global_row(prob, min(m0 + kBM, prob.M) - 1)) return;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {

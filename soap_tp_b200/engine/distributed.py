@@ -61,7 +61,7 @@ IDENTITY = IndexMap()
 
 
 def dist_gather(src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, cols_out: int, *, transpose: bool = False,
-                planes: Optional[k.Planes] = None, out: Optional[Tensor] = None) -> None:
+                planes: Optional[k.Planes] = None, out: Optional[Tensor] = None, upper_only: bool = False) -> None:
     """``out(i, j) = src(map_i(i), map_j(j))`` (``src(map_j(j), map_i(i))`` if ``transpose``)."""
     if rows_out <= 0 or cols_out <= 0:
         return
@@ -76,7 +76,7 @@ def dist_gather(src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, co
         src.segment.peer_table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
         map_i.p, map_i.P, map_i.nb, map_i.offset, map_i.perm.data_ptr() if map_i.perm is not None else 0,
         map_j.p, map_j.P, map_j.nb, map_j.offset, map_j.perm.data_ptr() if map_j.perm is not None else 0,
-        int(transpose), hi, lo, d_i, d_j, rows_out, cols_out, k._stream())
+        int(transpose), int(upper_only), hi, lo, d_i, d_j, rows_out, cols_out, k._stream())
     k._count("dist_gather_kernel")
     if out is not None:
         k.mark_written(out)
@@ -295,6 +295,7 @@ def gram_update(G_local: Tensor, preconditioner: Tensor, beta: float, block_size
     source = e.stage_shard(G_local, (rows, cols), shard_dim)
     e.comm.barrier()
     _gram_from_source(e, source, (rows, cols), preconditioner, beta, side)
+    _mirror_upper(e, [(side, preconditioner, size)])
     e.comm.barrier()
     return preconditioner
 
@@ -313,7 +314,25 @@ def _gram_from_source(e: GridEngine, source: Source, shape, preconditioner: Tens
         dist_gather(source, IDENTITY, e.row_map(), depth, lr, transpose=transpose, planes=a)
     b = e.planes("gram_b", depth, lc)
     dist_gather(source, IDENTITY, e.col_map(), depth, lc, transpose=transpose, planes=b)
-    k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta)
+    # only entries on or below the global diagonal are computed; `_mirror_upper` fills the rest
+    k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta,
+           lower_of_grid=(e.nb, e.pr, e.Pr, e.pc, e.Pc))
+
+
+def _mirror_upper(e: GridEngine, items) -> None:
+    """Complete symmetric packed matrices whose lower triangles were just computed.
+
+    ``items``: ``(tag, matrix, size)``.  Every rank publishes its packed block, and after one barrier
+    pulls the entries above the global diagonal from the owners of the mirrored entries (a transposed,
+    masked ``dist_gather``).  The result is exactly symmetric.  The published copies are overwritten
+    only after a later barrier of the caller.
+    """
+    sources = [e.stage_packed(f"gram_{tag}", matrix, (size, size)) for tag, matrix, size in items]
+    e.comm.barrier()
+    for source, (tag, matrix, size) in zip(sources, items):
+        lr, lc = e.rows_of(size), e.cols_of(size)
+        if lr and lc:
+            dist_gather(source, e.row_map(), e.col_map(), lr, lc, transpose=True, out=matrix[:lr, :lc], upper_only=True)
 
 
 def _gram_update_unequal(e: GridEngine, G_local, preconditioner, beta, shard_dim, side, dims) -> Tensor:
@@ -340,9 +359,11 @@ def _gram_update_unequal(e: GridEngine, G_local, preconditioner, beta, shard_dim
         a, b = e.planes("gram_a", depth, lr), e.planes("gram_b", depth, lc)
         dist_gather(source, IDENTITY, e.row_map(position), depth, lr, transpose=transpose, planes=a)
         dist_gather(source, IDENTITY, e.col_map(position), depth, lc, transpose=transpose, planes=b)
-        k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta)
+        k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta,
+               lower_of_grid=(e.nb, e.pr, e.Pr, e.pc, e.Pc))
     else:
         _gram_from_source(e, source, tuple(global_shape), preconditioner, beta, side)
+    _mirror_upper(e, [(side, preconditioner, true_size)])
     e.comm.barrier()
     return preconditioner
 
@@ -440,7 +461,7 @@ def _dist_gather_table(table: Tensor, src: Source, map_i: IndexMap, map_j: Index
     d_i = out.stride(0) if out.shape[0] > 1 else 1
     d_j = out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0])
     k._C.dist_gather(table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
-                     map_i.p, map_i.P, map_i.nb, map_i.offset, 0, map_j.p, map_j.P, map_j.nb, map_j.offset, 0, 0,
+                     map_i.p, map_i.P, map_i.nb, map_i.offset, 0, map_j.p, map_j.P, map_j.nb, map_j.offset, 0, 0, 0,
                      out.data_ptr(), 0, d_i, d_j, rows_out, cols_out, k._stream())
     k._count("dist_gather_kernel")
     k.mark_written(out)
@@ -532,6 +553,7 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
     if initializing:
         _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
         _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right")
+        _mirror_upper(e, [("left", state["left_preconditioner"], rows), ("right", state["right_preconditioner"], cols)])
         e.comm.barrier()
         initialize_bases(e, [
             (state[f"{side}_preconditioner"], state[f"{side}_basis"], size,
@@ -569,6 +591,7 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
     with TIMER.stage("gram", device):
         _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
         _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right", gathered=x_panel)
+        _mirror_upper(e, [("left", state["left_preconditioner"], rows), ("right", state["right_preconditioner"], cols)])
         e.comm.barrier()
     if step % interval == 0:
         with TIMER.stage("refresh", device):

@@ -155,6 +155,7 @@ def gemm(
     k_splits: int = 1,
     split_stride: int = 0,
     batch: Optional[dict] = None,
+    lower_of_grid: Optional[tuple] = None,
 ) -> None:
     """``acc[m, n] = sum_k a[k, m] * b[k, n]`` then the fused epilogue (see ``csrc/gemm.h``).
 
@@ -192,11 +193,20 @@ def gemm(
         ibc1, isbc2 = 1.0 / adam["bias_correction1"], 1.0 / math.sqrt(adam["bias_correction2"])
     status = status_word(a.hi.device)
     _C.gemm_tf32x3(a.hi.data_ptr(), a.lo.data_ptr(), a.ld, b.hi.data_ptr(), b.lo.data_ptr(), b.ld, M, N, K,
-                   mode, int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
+                   mode, 2 if lower_of_grid is not None else int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
                    mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, int(k_splits), int(split_stride), status.data_ptr(),
-                   _stream(), **_batch_arguments(a, b, batch))
+                   _stream(), **_batch_arguments(a, b, batch), **_triangle_arguments(lower_of_grid))
     mark_written(out, momentum, variance)
     _count("gemm_tf32x3_kernel")
+
+
+def _triangle_arguments(lower_of_grid: Optional[tuple]) -> dict:
+    """``(block_size, pr, Pr, pc, Pc)``: produce only the entries of this rank's packed block that lie on or
+    below the global diagonal of a symmetric result."""
+    if lower_of_grid is None:
+        return {}
+    nb, pr, Pr, pc, Pc = lower_of_grid
+    return dict(tri_nb=int(nb), tri_pr=int(pr), tri_Pr=int(Pr), tri_pc=int(pc), tri_Pc=int(Pc))
 
 
 def _batch_arguments(a: "Planes", b: "Planes", batch: Optional[dict]) -> dict:
