@@ -34,7 +34,7 @@ def timed(fn, repeats: int) -> float:
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("case", choices=("gemm", "qr", "panel", "update", "adam", "split"))
+    parser.add_argument("case", choices=("gemm", "qr", "qrpair", "panel", "update", "adam", "split"))
     parser.add_argument("--size", type=int, default=4096)
     parser.add_argument("--rows", type=int, default=4096)
     parser.add_argument("--mode", default="store")
@@ -70,6 +70,10 @@ def main(argv=None) -> int:
         matrix, Q = rand(n, n).T, torch.empty(n, n, device=device).T
         us = timed(lambda: qr.householder_qr(matrix.clone(), Q), args.repeats)
         print(f"householder_qr {n}: {us / 1e3:.2f} ms")
+    elif args.case == "qrpair":
+        jobs = [(rand(n, n).T, torch.empty(n, n, device=device).T, None) for _ in range(2)]
+        us = timed(lambda: qr.householder_qr_pair(jobs), args.repeats)
+        print(f"householder_qr_pair 2 x {n}: {us / 1e3:.2f} ms")
     elif args.case in ("panel", "update"):
         ws = qr._workspace(max(n, args.rows), device)
         k.split_planes(rand(max(n, args.rows), max(n, args.rows)), out=ws["C"])

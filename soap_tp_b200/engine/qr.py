@@ -15,6 +15,7 @@ needed between panels.  All arithmetic is fp32-class (3xTF32 products, fp32 pane
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
@@ -86,6 +87,14 @@ def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = N
 
 
 _SIDE_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
+_PANEL_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
+
+
+def _panel_stream(device, slot: int) -> "torch.cuda.Stream":
+    key = (str(device), slot)
+    if key not in _PANEL_STREAMS:
+        _PANEL_STREAMS[key] = torch.cuda.Stream(device=device, priority=-1)
+    return _PANEL_STREAMS[key]
 
 
 def householder_qr_pair(jobs) -> None:
@@ -140,26 +149,64 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
     k.split_planes(source, out=C)
     stream = k._stream
     panels = list(range(0, n, PANEL))
-    for p, j0 in enumerate(panels):
+    main = torch.cuda.current_stream(device)
+    side = _panel_stream(device, slot) if os.environ.get("SOAP_TP_QR_LOOKAHEAD", "1") != "0" else main
+
+    def launch_panel(p: int, after: "torch.cuda.Event") -> "torch.cuda.Event":
+        """Panel ``p`` on the panel stream, once ``after`` has happened; returns its completion event."""
+        j0 = panels[p]
         bw, r = min(PANEL, n - j0), n - j0
-        nc = n - j0 - bw
         panel, v, vt = C.sub(j0, j0, r, bw), V.sub(j0, j0, r, bw), ws["Vt"][p]
         tau = ws["tau"][j0:]
         T, Tt = ws["T"][p], ws["Tt"][p]
-        _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(), v.ld,
-                    vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(), T.lo.data_ptr(),
-                    Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
-                    k.status_word(device).data_ptr(), stream())
-        k._count("qr_panel_kernel")
+        side.wait_event(after)
+        with torch.cuda.stream(side):
+            _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(),
+                        v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(),
+                        T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                        k.status_word(device).data_ptr(), stream())
+            k._count("qr_panel_kernel")
+            done = torch.cuda.Event()
+            done.record(side)
+        return done
+
+    def update(p: int, first_col: int, count: int) -> None:
+        """Apply the block reflector of panel ``p`` to ``count`` columns starting at ``first_col``."""
+        j0 = panels[p]
+        bw, r = min(PANEL, n - j0), n - j0
+        v = V.sub(j0, j0, r, bw)
+        z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else ws["Z_last"]
+        w = ws["W"].sub(0, 0, bw, count)
+        block = C.sub(j0, first_col, r, count)
+        _skinny_product(ws, v, block, w)                                                    # W = V^T C
+        k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0)               # C -= Z^T W
+
+    # Look-ahead: as soon as the reflector of panel p has been applied to the columns of panel p + 1,
+    # that panel is factored on a second (high-priority) stream while this stream applies the reflector
+    # to the remaining columns.  The latency-bound panel kernel occupies a few dozen SMs; the
+    # tensor-core updates use the others.
+    start = torch.cuda.Event()
+    start.record(main)
+    done = launch_panel(0, start)
+    for p, j0 in enumerate(panels):
+        bw, r = min(PANEL, n - j0), n - j0
+        nc = n - j0 - bw
+        main.wait_event(done)
         if nc > 0:
+            vt, Tt = ws["Vt"][p], ws["Tt"][p]
             t_op = k.Planes(Tt.hi, Tt.lo, bw, bw, Tt.ld)
             vt_op = vt.sub(0, 0, bw, r)
-            z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else k.Planes.empty(bw, r, device)
+            if bw != PANEL:
+                ws["Z_last"] = k.Planes.empty(bw, r, device)
+            z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else ws["Z_last"]
             k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z, force_narrow=True)            # Z = T V^T
-            w = ws["W"].sub(0, 0, bw, nc) if bw == PANEL else k.Planes.empty(bw, nc, device)
-            trailing = C.sub(j0, j0 + bw, r, nc)
-            _skinny_product(ws, v, trailing, w)                                             # W = V^T C
-            k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=trailing, alpha=-1.0, beta=1.0)        # C -= Z^T W
+            ahead = min(PANEL, nc)
+            update(p, j0 + bw, ahead)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            done = launch_panel(p + 1, ready)
+            if nc > ahead:
+                update(p, j0 + bw + ahead, nc - ahead)
         yield
     # explicit Q = H_0 H_1 ... applied to the identity, last panel first
     _C.identity_planes(Qp.hi.data_ptr(), Qp.lo.data_ptr(), Qp.ld, n, n, stream())
