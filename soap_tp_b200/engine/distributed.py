@@ -300,6 +300,39 @@ def gram_update(G_local: Tensor, preconditioner: Tensor, beta: float, block_size
     return preconditioner
 
 
+def gram_rows_from_col_shards(G_local: Tensor, out: Tensor, beta: float, side: str) -> Tensor:
+    """1-D row-sharded Gram EMA for column-sharded ``G`` (``ops/gram_1d.py``).
+
+    ``side == "left"``: ``out`` is rows ``[r m/W, (r+1) m/W)`` of ``beta L + (1-beta) G G^T``;
+    ``side == "right"``: the block row of ``G^T G`` of this rank's columns.  ``out`` is row-major, so
+    its memory is the column-major transpose ``C' = (all rows) x (my rows)`` that the GEMM writes.
+    """
+    world = dist.get_world_size()
+    e = engine_for(G_local.device, (1, world), 128)
+    shape = torch.tensor(list(G_local.shape), dtype=torch.int64)
+    shapes = [torch.empty_like(shape) for _ in range(world)]
+    dist.all_gather(shapes, shape, group=e.comm.control)
+    if any(s.tolist() != shapes[0].tolist() for s in shapes):
+        raise RuntimeError("every rank must hold a column shard of the same shape.")
+    m, n_local = G_local.shape
+    n = n_local * world
+    source = e.stage_shard(G_local, (m, n), 1)
+    e.comm.barrier()
+    if side == "left":
+        depth, size, mine, first = n, m, m // world, e.rank * (m // world)
+        a = e.planes("gram1d_left", depth, size)
+        dist_gather(source, IDENTITY, IDENTITY, depth, size, transpose=True, planes=a)   # G^T
+    else:
+        depth, size, mine, first = m, n, n_local, e.rank * n_local
+        a = e.planes("gram1d_right", depth, size)
+        dist_gather(source, IDENTITY, IDENTITY, depth, size, planes=a)                   # G
+    b = a.sub(0, first, depth, mine)
+    k.gemm(a, b, out=out.T, alpha=1.0 - beta, beta=beta)
+    k.mark_written(out)
+    e.comm.barrier()
+    return out
+
+
 def _gram_from_source(e: GridEngine, source: Source, shape, preconditioner: Tensor, beta: float, side: str,
                       gathered: Optional[k.Planes] = None) -> None:
     rows, cols = shape

@@ -296,3 +296,28 @@ def case_batch(rank, world, device_kind, specs):
         except Exception as error:  # re-raise with the spec for a readable report
             raise AssertionError(f"{name}{args}: {type(error).__name__}: {error}") from error
         dist.barrier()
+
+
+def case_gram_1d(rank, world, device_kind, shape, beta):
+    """Row-sharded Gram updates for column-sharded gradients against the dense products."""
+    from soap_tp_b200.ops.gram_1d import (update_left_preconditioner_from_col_shards,
+                                          update_right_preconditioner_from_col_shards)
+
+    device = dev(device_kind, rank)
+    rows, cols = shape
+    full = seeded(shape, 21)
+    shard = full.chunk(world, dim=1)[rank].contiguous().to(device)
+    L0, R0 = spd(rows, 22), spd(cols, 23)
+    rows_here, cols_here = rows // world, cols // world
+    L = L0[rank * rows_here:(rank + 1) * rows_here].clone().to(device)
+    R = R0[rank * cols_here:(rank + 1) * cols_here].clone().to(device)
+    out = update_left_preconditioner_from_col_shards(shard, L, beta)
+    assert out is L
+    update_right_preconditioner_from_col_shards(shard, R, beta)
+    fd = full.double()
+    eL = (beta * L0.double() + (1 - beta) * fd @ fd.T)[rank * rows_here:(rank + 1) * rows_here]
+    eR = (beta * R0.double() + (1 - beta) * fd.T @ fd)[rank * cols_here:(rank + 1) * cols_here]
+    assert relative_l2(L.cpu().double(), eL) < 1e-5
+    assert relative_l2(R.cpu().double(), eR) < 1e-5
+    fresh = update_left_preconditioner_from_col_shards(shard, None, 0.0)
+    assert relative_l2(fresh.cpu().double(), (fd @ fd.T)[rank * rows_here:(rank + 1) * rows_here]) < 1e-5

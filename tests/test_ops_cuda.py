@@ -52,6 +52,7 @@ def test_four_ranks_ops():
               ("case_redistribute", ((300, 200), 64, GRID4, 1))]
     specs += [("case_gram", (shape, 2, GRID4, sd, 0.0)) for shape in RECT for sd in (0, 1)]
     specs += [("case_gram", ((9, 13), 2, GRID4, 1, 0.25)), ("case_gram", ((300, 520), 64, GRID4, 1, 0.25))]
+    specs += [("case_gram_1d", ((8, 12), 0.0)), ("case_gram_1d", ((300, 520), 0.25))]
     specs += [("case_rotate", (shape, 2, GRID4)) for shape in RECT] + [("case_rotate", ((260, 390), 64, GRID4))]
     specs += [("case_permute", ((9, 13), 2, GRID4)), ("case_permute", ((200, 300), 64, GRID4))]
     specs += [("case_power_iteration_qr", (n, 2, GRID4)) for n in (8, 9, 13)]

@@ -26,6 +26,7 @@ def test_redistribution():
 def test_gram_updates():
     specs = [("case_gram", (shape, 2, GRID, sd, 0.0)) for shape in RECT for sd in (0, 1)]
     specs.append(("case_gram", ((9, 13), 2, GRID, 1, 0.25)))      # beta and initial value
+    specs += [("case_gram_1d", ((8, 12), 0.0)), ("case_gram_1d", ((12, 8), 0.25))]   # 1-D row-sharded results
     run_distributed(cases.case_batch, 4, "cpu", specs)
 
 
@@ -48,6 +49,7 @@ def test_single_rank_grid():
     run_distributed(cases.case_batch, 1, "cpu", [
         ("case_rotate", ((9, 13), 4, (1, 1))), ("case_refresh", ((8, 12), 3, (1, 1))),
         ("case_gram", ((9, 13), 4, (1, 1), 1, 0.5)), ("case_redistribute", ((9, 13), 4, (1, 1), 0)),
+        ("case_gram_1d", ((9, 13), 0.5)),
     ])
 
 
