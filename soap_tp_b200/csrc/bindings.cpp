@@ -40,7 +40,7 @@ PYBIND11_MODULE(_C, m) {
          uint64_t stream, int batches, int a_k_step, int a_row_step, int b_k_step, int b_row_step,
          int64_t c_batch_stride, int64_t a_k_total, int64_t a_rows_total, int64_t b_k_total, int64_t b_rows_total,
          uint64_t remap, uint64_t C2hi, uint64_t C2lo, int64_t ld2, int m_limit, int o1_row_start, int tri_nb,
-         int tri_pr, int tri_Pr, int tri_pc, int tri_Pc) {
+         int tri_pr, int tri_Pr, int tri_pc, int tri_Pc, int tri_m0, int tri_n0) {
         GemmOperands ops{};
         ops.a_hi = ptr<const float>(a_hi); ops.a_lo = ptr<const float>(a_lo); ops.lda = lda;
         ops.b_hi = ptr<const float>(b_hi); ops.b_lo = ptr<const float>(b_lo); ops.ldb = ldb;
@@ -61,7 +61,7 @@ PYBIND11_MODULE(_C, m) {
         prob.remap = ptr<const int>(remap); prob.C2hi = ptr<float>(C2hi); prob.C2lo = ptr<float>(C2lo);
         prob.ld2 = ld2; prob.m_limit = m_limit; prob.o1_row_start = o1_row_start;
         prob.tri_nb = tri_nb > 0 ? tri_nb : 1; prob.tri_pr = tri_pr; prob.tri_Pr = tri_Pr > 0 ? tri_Pr : 1;
-        prob.tri_pc = tri_pc; prob.tri_Pc = tri_Pc > 0 ? tri_Pc : 1;
+        prob.tri_pc = tri_pc; prob.tri_Pc = tri_Pc > 0 ? tri_Pc : 1; prob.tri_m0 = tri_m0; prob.tri_n0 = tri_n0;
         py::gil_scoped_release release;
         gemm_tf32x3(ops, prob, ptr<int>(status), stream_of(stream));
       },
@@ -74,7 +74,7 @@ PYBIND11_MODULE(_C, m) {
       py::arg("b_k_step") = 0, py::arg("b_row_step") = 0, py::arg("c_batch_stride") = 0, py::arg("a_k_total") = 0,
       py::arg("a_rows_total") = 0, py::arg("b_k_total") = 0, py::arg("b_rows_total") = 0, py::arg("remap") = 0,
       py::arg("C2hi") = 0, py::arg("C2lo") = 0, py::arg("ld2") = 0, py::arg("m_limit") = 0, py::arg("o1_row_start") = 0, py::arg("tri_nb") = 1, py::arg("tri_pr") = 0,
-      py::arg("tri_Pr") = 1, py::arg("tri_pc") = 0, py::arg("tri_Pc") = 1,
+      py::arg("tri_Pr") = 1, py::arg("tri_pc") = 0, py::arg("tri_Pc") = 1, py::arg("tri_m0") = 0, py::arg("tri_n0") = 0,
       "3xTF32 tcgen05 GEMM acc[m,n] = sum_k Za[k,m] Zb[k,n] with fused epilogue");
 
   m.def("gemm_simt",

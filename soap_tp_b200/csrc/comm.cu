@@ -56,9 +56,11 @@ struct IndexMap {
   int p, P, nb;               // local -> global: g = ((l / nb) * P + p) * nb + l % nb   (P == 1: identity)
   int offset;                 // then g <- g + offset
   const int64_t* perm;        // optional, last: g <- perm[g]
+  int local_offset;           // first of all: l <- l + local_offset (a chunk of the local index range)
 };
 
 __device__ __forceinline__ int map_index(const IndexMap& map, int local) {
+  local += map.local_offset;
   int g = local;
   if (map.P > 1) g = ((local / map.nb) * map.P + map.p) * map.nb + local % map.nb;
   g += map.offset;
@@ -194,12 +196,12 @@ void register_comm(py::module_& m) {
   m.def("dist_gather",
         [](uint64_t peers, int kind, int rows, int cols, int nb_r, int nb_c, int Pr, int Pc, int world, int ip, int iP,
            int inb, int ioff, uint64_t iperm, int jp, int jP, int jnb, int joff, uint64_t jperm, int transpose,
-           int upper_only, uint64_t out_hi, uint64_t out_lo,
+           int upper_only, int i_local_offset, int j_local_offset, uint64_t out_hi, uint64_t out_lo,
            int64_t d_i, int64_t d_j, int rows_out, int cols_out, uint64_t stream) {
           if (rows_out <= 0 || cols_out <= 0) return;
           DistSource src{reinterpret_cast<const float* const*>(peers), kind, rows, cols, nb_r, nb_c, Pr, Pc, world};
-          IndexMap mi{ip, iP, inb, ioff, reinterpret_cast<const int64_t*>(iperm)};
-          IndexMap mj{jp, jP, jnb, joff, reinterpret_cast<const int64_t*>(jperm)};
+          IndexMap mi{ip, iP, inb, ioff, reinterpret_cast<const int64_t*>(iperm), i_local_offset};
+          IndexMap mj{jp, jP, jnb, joff, reinterpret_cast<const int64_t*>(jperm), j_local_offset};
           // consecutive i are consecutive in the source when i indexes the source's contiguous dimension:
           // rows for column-major packed buffers, columns for row-major shards.
           const bool i_is_source_row = !transpose;

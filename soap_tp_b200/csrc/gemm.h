@@ -33,6 +33,7 @@ struct GemmProblem {
   int symmetric;     // 1: A == B, compute tiles on/below the diagonal and mirror the rest (kEpiStore only);
                      // 2: packed block-cyclic part of a symmetric result, entries on/below the GLOBAL diagonal only
   int tri_nb, tri_pr, tri_Pr, tri_pc, tri_Pc;   // symmetric == 2: block size and grid coordinates of this rank
+  int tri_m0, tri_n0;                           // symmetric == 2: local row / column index of output element (0, 0)
   int force_narrow;  // use 128-wide tiles regardless of the problem size
   int k_splits;      // kEpiStore: split K over this many CTAs per tile, partial s written at C + s*split_stride
   int64_t split_stride;

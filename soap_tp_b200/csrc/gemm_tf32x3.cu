@@ -80,10 +80,14 @@ __device__ __forceinline__ float tf32_round(float x) {
 // matrix; only entries on or below the GLOBAL diagonal are produced (the rest is pulled from the
 // peers that own the mirrored entries).
 __device__ __forceinline__ int global_row(const GemmProblem& p, int m) {
-  return p.symmetric == 2 ? ((m / p.tri_nb) * p.tri_Pr + p.tri_pr) * p.tri_nb + m % p.tri_nb : m;
+  if (p.symmetric != 2) return m;
+  m += p.tri_m0;
+  return ((m / p.tri_nb) * p.tri_Pr + p.tri_pr) * p.tri_nb + m % p.tri_nb;
 }
 __device__ __forceinline__ int global_col(const GemmProblem& p, int n) {
-  return p.symmetric == 2 ? ((n / p.tri_nb) * p.tri_Pc + p.tri_pc) * p.tri_nb + n % p.tri_nb : n;
+  if (p.symmetric != 2) return n;
+  n += p.tri_n0;
+  return ((n / p.tri_nb) * p.tri_Pc + p.tri_pc) * p.tri_nb + n % p.tri_nb;
 }
 
 constexpr int kTilePitch = kBM + 4;   // floats between columns of the staged tile (keeps 16-byte alignment)
@@ -220,7 +224,7 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
     }
     return;
   }
-  bool vector = rows == kBM && !(prob.symmetric == 2 && (prob.tri_nb & 3) != 0);
+  bool vector = rows == kBM && !(prob.symmetric == 2 && ((prob.tri_nb | prob.tri_m0) & 3) != 0);
   if constexpr (MODE == kEpiStore) vector = vector && aligned16(prob.C + c_shift, prob.ldc);
   if constexpr (MODE == kEpiSplit)
     vector = vector && aligned16(prob.Chi, prob.ldp) && aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);

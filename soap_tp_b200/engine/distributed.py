@@ -17,6 +17,7 @@ Ordering between ranks is one barrier per producer/consumer edge (see ``parallel
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Any, Dict, MutableMapping, Optional, Tuple
 
@@ -31,6 +32,10 @@ from . import factor
 from . import kernels as k
 
 KIND_BLOCK_CYCLIC, KIND_ROW_SHARDS, KIND_COL_SHARDS = 0, 1, 2
+# Overlap peer pulls with the products that consume them (SOAP_TP_PIPELINE_GATHERS=0: one pull, one product).
+PIPELINE_GATHERS = os.environ.get("SOAP_TP_PIPELINE_GATHERS", "1") != "0"
+# output tiles a chunk must keep (about one wave of the 148 SMs); tests lower it to chunk small problems
+PIPELINE_MIN_TILES = max(1, int(os.environ.get("SOAP_TP_PIPELINE_MIN_TILES", "120")))
 
 
 @dataclass
@@ -55,6 +60,7 @@ class IndexMap:
     nb: int = 1
     offset: int = 0
     perm: Optional[Tensor] = None
+    local_offset: int = 0   # added to the local index before anything else (a chunk of the local range)
 
 
 IDENTITY = IndexMap()
@@ -76,7 +82,8 @@ def dist_gather(src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, co
         src.segment.peer_table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
         map_i.p, map_i.P, map_i.nb, map_i.offset, map_i.perm.data_ptr() if map_i.perm is not None else 0,
         map_j.p, map_j.P, map_j.nb, map_j.offset, map_j.perm.data_ptr() if map_j.perm is not None else 0,
-        int(transpose), int(upper_only), hi, lo, d_i, d_j, rows_out, cols_out, k._stream())
+        int(transpose), int(upper_only), map_i.local_offset, map_j.local_offset, hi, lo, d_i, d_j, rows_out, cols_out,
+        k._stream())
     k._count("dist_gather_kernel")
     if out is not None:
         k.mark_written(out)
@@ -184,25 +191,100 @@ class GridEngine:
         return plain, transposed
 
     # ---- two chained stationary-C products ---------------------------------------------------
-    def two_sided(self, source: Source, shape, first: k.Planes, second: k.Planes, *, gathered: Optional[k.Planes] = None,
-                  **final) -> k.Planes:
+    # ---- gather / product pipelining ------------------------------------------------------------
+    def _pipeline_streams(self):
+        if not hasattr(self, "_gather_stream"):
+            self._gather_stream = torch.cuda.Stream(device=self.device)
+            self._product_stream = torch.cuda.Stream(device=self.device)
+        return self._gather_stream, self._product_stream
+
+    @staticmethod
+    def _column_chunks(cols: int, tiles: int, granule: int):
+        """Split ``cols`` operand columns into up to four chunks (boundaries on multiples of ``granule``) such
+        that each chunk still launches about a wave of the ``tiles`` output tiles of the whole product."""
+        slabs = -(-cols // granule)
+        count = max(1, min(4, tiles // PIPELINE_MIN_TILES, slabs))
+        if not PIPELINE_GATHERS or count == 1:
+            return [(0, cols)]
+        bounds = [granule * ((slabs * i) // count) for i in range(count)] + [cols]
+        return [(bounds[i], bounds[i + 1]) for i in range(count) if bounds[i + 1] > bounds[i]]
+
+    def gather_then_multiply(self, source: Source, column_map: IndexMap, depth: int, cols: int, planes: k.Planes,
+                             multiply, *, transpose: bool = False, other_cols: int = 256, as_columns: bool = False) -> None:
+        """Pull the operand ``planes`` (``depth x cols``; local column ``j`` is source column ``column_map(j)``)
+        from the peers chunk by chunk and call ``multiply(c0, c1)`` for every chunk once it has landed.
+
+        The pulls run on a stream of their own and the products alternate between the calling stream and a
+        second one, so the NVLink transfer of chunk ``i + 1`` overlaps the tensor-core product of chunk
+        ``i`` and consecutive products fill each other's tails.  ``multiply(c0, c1)`` must touch only rows
+        ``[c0, c1)`` of its outputs (columns, with ``as_columns``: the operand is the product's second one);
+        ``other_cols`` is the extent of the product's other output dimension.
+        """
+        if as_columns:
+            tiles, granule = -(-other_cols // 128) * -(-cols // 256), 256
+        else:
+            tiles, granule = -(-cols // 128) * -(-other_cols // 256), 128
+        chunks = self._column_chunks(cols, tiles, granule)
+        if len(chunks) == 1:
+            dist_gather(source, IDENTITY, column_map, depth, cols, transpose=transpose, planes=planes)
+            multiply(0, cols)
+            return
+        main = torch.cuda.current_stream(self.device)
+        pulls, second = self._pipeline_streams()
+        start = torch.cuda.Event()
+        start.record(main)
+        pulls.wait_event(start)
+        second.wait_event(start)
+        for index, (c0, c1) in enumerate(chunks):
+            with torch.cuda.stream(pulls):
+                chunk_map = IndexMap(column_map.p, column_map.P, column_map.nb, column_map.offset, column_map.perm,
+                                     column_map.local_offset + c0)
+                dist_gather(source, IDENTITY, chunk_map, depth, c1 - c0, transpose=transpose,
+                            planes=planes.sub(0, c0, depth, c1 - c0))
+                landed = torch.cuda.Event()
+                landed.record(pulls)
+            target = main if index % 2 == 0 else second
+            target.wait_event(landed)
+            with torch.cuda.stream(target):
+                multiply(c0, c1)
+        joined = torch.cuda.Event()
+        joined.record(second)
+        main.wait_event(joined)
+
+    def two_sided(self, source: Source, shape, first: k.Planes, second: k.Planes, *, panel: Optional[k.Planes] = None,
+                  gathered: bool = False, **final) -> k.Planes:
         """``final( (X^T F)^T S )`` for the ``rows x cols`` matrix ``X`` behind ``source``.
 
         ``first`` holds ``F[:, my column class]`` (depth rows), ``second`` holds ``S[:, my column
-        class]`` (depth cols).  The caller has already ordered ``source`` before this call.  Returns
-        the gathered operand planes of ``X`` (``X[:, my row class]``) for reuse.
+        class]`` (depth cols).  The caller has already ordered ``source`` before this call.  ``panel``
+        is the buffer for the gathered operand ``X[:, my row class]`` (``gathered``: it already holds it);
+        it is returned for reuse.  Both pulls are pipelined with their products.
         """
         rows, cols = shape
-        a = gathered
-        if a is None:
-            a = self.planes("panel_a", rows, self.rows_of(cols))
-            dist_gather(source, IDENTITY, self.row_map(), rows, self.rows_of(cols), planes=a)
+        a = panel if panel is not None else self.planes("panel_a", rows, self.rows_of(cols))
         _, t_view, t_source = self.packed_segment("middle", (cols, rows))
-        k.gemm(a, first, mode=k.EPI_STORE, out=t_view[: max(1, a.cols), : max(1, first.cols)])
+        first_cols = max(1, first.cols)
+
+        def middle(c0: int, c1: int) -> None:
+            k.gemm(a.sub(0, c0, rows, c1 - c0), first, mode=k.EPI_STORE, out=t_view[c0:c1, :first_cols])
+
+        if a.cols > 0:
+            if gathered:
+                middle(0, a.cols)
+            else:
+                self.gather_then_multiply(source, self.row_map(), rows, a.cols, a, middle, other_cols=first.cols)
         self.comm.barrier()
         ta = self.planes("panel_t", cols, self.rows_of(rows))
-        dist_gather(t_source, IDENTITY, self.row_map(), cols, self.rows_of(rows), planes=ta)
-        k.gemm(ta, second, **final)
+
+        def last(c0: int, c1: int) -> None:
+            window = dict(final)
+            for name in ("out", "momentum", "variance"):
+                if window.get(name) is not None:
+                    window[name] = window[name][c0:c1]
+            k.gemm(ta.sub(0, c0, cols, c1 - c0), second, **window)
+
+        if ta.cols > 0:
+            self.gather_then_multiply(t_source, self.row_map(), cols, ta.cols, ta, last, other_cols=second.cols)
         return a
 
 
@@ -335,21 +417,41 @@ def gram_rows_from_col_shards(G_local: Tensor, out: Tensor, beta: float, side: s
 
 def _gram_from_source(e: GridEngine, source: Source, shape, preconditioner: Tensor, beta: float, side: str,
                       gathered: Optional[k.Planes] = None) -> None:
+    """Lower triangle (global indices) of ``beta P + (1 - beta) Gram`` on this rank's packed block.
+
+    Operand panels: ``a`` = the Gram factor restricted to my local rows, ``b`` = to my local columns;
+    ``gathered`` is ``a`` if the caller already holds it.  Whichever operand still has to come from the
+    peers last is pulled in chunks that overlap with the products; `_mirror_upper` fills the other triangle.
+    """
     rows, cols = shape
     if side == "left":    # L = G G^T: contraction over columns, operands are rows of G
         size, depth, transpose = rows, cols, True
     else:                 # R = G^T G: contraction over rows, operands are columns of G
         size, depth, transpose = cols, rows, False
     lr, lc = e.rows_of(size), e.cols_of(size)
-    a = gathered
-    if a is None:
-        a = e.planes("gram_a", depth, lr)
-        dist_gather(source, IDENTITY, e.row_map(), depth, lr, transpose=transpose, planes=a)
+    if lr == 0 or lc == 0:
+        return
+    triangle = (e.nb, e.pr, e.Pr, e.pc, e.Pc)
+    weight = dict(alpha=1.0 - beta, beta=beta)
     b = e.planes("gram_b", depth, lc)
+    if gathered is not None:
+        a = gathered
+
+        def columns(c0: int, c1: int) -> None:     # a window of my local columns
+            k.gemm(a, b.sub(0, c0, depth, c1 - c0), out=preconditioner[:lr, c0:c1], lower_of_grid=triangle + (0, c0),
+                   **weight)
+
+        e.gather_then_multiply(source, e.col_map(), depth, lc, b, columns, transpose=transpose, other_cols=lr,
+                               as_columns=True)
+        return
+    a = e.planes("gram_a", depth, lr)
     dist_gather(source, IDENTITY, e.col_map(), depth, lc, transpose=transpose, planes=b)
-    # only entries on or below the global diagonal are computed; `_mirror_upper` fills the rest
-    k.gemm(a, b, out=preconditioner[: max(1, lr), : max(1, lc)], alpha=1.0 - beta, beta=beta,
-           lower_of_grid=(e.nb, e.pr, e.Pr, e.pc, e.Pc))
+
+    def rows_window(c0: int, c1: int) -> None:      # a window of my local rows
+        k.gemm(a.sub(0, c0, depth, c1 - c0), b, out=preconditioner[c0:c1, :lc], lower_of_grid=triangle + (c0, 0),
+               **weight)
+
+    e.gather_then_multiply(source, e.row_map(), depth, lr, a, rows_window, transpose=transpose, other_cols=lc)
 
 
 def _mirror_upper(e: GridEngine, items) -> None:
@@ -494,7 +596,7 @@ def _dist_gather_table(table: Tensor, src: Source, map_i: IndexMap, map_j: Index
     d_i = out.stride(0) if out.shape[0] > 1 else 1
     d_j = out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0])
     k._C.dist_gather(table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
-                     map_i.p, map_i.P, map_i.nb, map_i.offset, 0, map_j.p, map_j.P, map_j.nb, map_j.offset, 0, 0, 0,
+                     map_i.p, map_i.P, map_i.nb, map_i.offset, 0, map_j.p, map_j.P, map_j.nb, map_j.offset, 0, 0, 0, 0, 0,
                      out.data_ptr(), 0, d_i, d_j, rows_out, cols_out, k._stream())
     k._count("dist_gather_kernel")
     k.mark_written(out)
@@ -608,8 +710,7 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
     with TIMER.stage("rotate_forward+adam", device):
         _, u_view, u_source = e.packed_segment("update", global_shape)
         x_panel = e.planes("x_panel", rows, e.rows_of(cols))   # X[:, my row class]; reused by the right Gram
-        dist_gather(shard_source, IDENTITY, e.row_map(), rows, e.rows_of(cols), planes=x_panel)
-        e.two_sided(shard_source, global_shape, left_plain, right_plain, gathered=x_panel, mode=k.EPI_ADAM,
+        e.two_sided(shard_source, global_shape, left_plain, right_plain, panel=x_panel, mode=k.EPI_ADAM,
                     out=u_view[: max(1, lr), : max(1, lc)],
                     momentum=state["momentum"][: max(1, lr), : max(1, lc)],
                     variance=state["variance"][: max(1, lr), : max(1, lc)], adam=adam)

@@ -201,12 +201,15 @@ def gemm(
 
 
 def _triangle_arguments(lower_of_grid: Optional[tuple]) -> dict:
-    """``(block_size, pr, Pr, pc, Pc)``: produce only the entries of this rank's packed block that lie on or
-    below the global diagonal of a symmetric result."""
+    """``(block_size, pr, Pr, pc, Pc[, m0, n0])``: produce only the entries of this rank's packed block that
+    lie on or below the global diagonal of a symmetric result; ``m0, n0`` is the local index of the output's
+    first element when the output is a window of the packed block."""
     if lower_of_grid is None:
         return {}
-    nb, pr, Pr, pc, Pc = lower_of_grid
-    return dict(tri_nb=int(nb), tri_pr=int(pr), tri_Pr=int(Pr), tri_pc=int(pc), tri_Pc=int(Pc))
+    nb, pr, Pr, pc, Pc = lower_of_grid[:5]
+    m0, n0 = (lower_of_grid[5], lower_of_grid[6]) if len(lower_of_grid) > 5 else (0, 0)
+    return dict(tri_nb=int(nb), tri_pr=int(pr), tri_Pr=int(Pr), tri_pc=int(pc), tri_Pc=int(Pc), tri_m0=int(m0),
+                tri_n0=int(n0))
 
 
 def _batch_arguments(a: "Planes", b: "Planes", batch: Optional[dict]) -> dict:

@@ -76,3 +76,15 @@ def test_two_ranks_and_eight_ranks():
         ("case_soap_trajectory", ((12, 12), 2, (1, 2), 1) + TINY)])
     run_distributed(cases.case_batch, 8, "cuda", [
         ("case_rotate", ((40, 24), 4, (2, 4))), ("case_soap_trajectory", ((16, 16), 2, (2, 4), 1) + TINY)])
+
+
+def test_chunked_gather_product_pipeline(monkeypatch):
+    """Force the peer pulls to be split into chunks that overlap with their products (as they are at
+    8192 on real grids) on shapes small enough for a shared test GPU; compare with the dense oracle."""
+    monkeypatch.setenv("SOAP_TP_PIPELINE_MIN_TILES", "1")
+    big = (10, 3, (0.8, 0.9), 0.75, 1e-6, 1e-5, "eigh", 2.0, 3e-6)
+    for world, grid in ((4, GRID4), (2, (1, 2))):
+        run_distributed(cases.case_batch, world, "cuda", [
+            ("case_gram", ((600, 520), 64, grid, 1, 0.25)), ("case_gram", ((520, 650), 128, grid, 0, 0.5)),
+            ("case_rotate", ((520, 650), 64, grid)),
+            ("case_soap_trajectory", ((384, 384), 64, grid, 1) + big)])
