@@ -32,8 +32,10 @@ from . import factor
 from . import kernels as k
 
 KIND_BLOCK_CYCLIC, KIND_ROW_SHARDS, KIND_COL_SHARDS = 0, 1, 2
-# Overlap peer pulls with the products that consume them (SOAP_TP_PIPELINE_GATHERS=0: one pull, one product).
-PIPELINE_GATHERS = os.environ.get("SOAP_TP_PIPELINE_GATHERS", "1") != "0"
+# SOAP_TP_PIPELINE_GATHERS=1 overlaps peer pulls with the products that consume them, chunk by chunk.  Off by
+# default: at 8192 on 2 B200s it measured 23.8-24.0 ms/step against 23.2-23.5 with one pull and one product --
+# under the 1 kW power cap the product slows down by what the overlap hides, and chunking adds partial waves.
+PIPELINE_GATHERS = os.environ.get("SOAP_TP_PIPELINE_GATHERS", "0") == "1"
 # output tiles a chunk must keep (about one wave of the 148 SMs); tests lower it to chunk small problems
 PIPELINE_MIN_TILES = max(1, int(os.environ.get("SOAP_TP_PIPELINE_MIN_TILES", "120")))
 

@@ -81,6 +81,7 @@ def test_two_ranks_and_eight_ranks():
 def test_chunked_gather_product_pipeline(monkeypatch):
     """Force the peer pulls to be split into chunks that overlap with their products (as they are at
     8192 on real grids) on shapes small enough for a shared test GPU; compare with the dense oracle."""
+    monkeypatch.setenv("SOAP_TP_PIPELINE_GATHERS", "1")
     monkeypatch.setenv("SOAP_TP_PIPELINE_MIN_TILES", "1")
     big = (10, 3, (0.8, 0.9), 0.75, 1e-6, 1e-5, "eigh", 2.0, 3e-6)
     for world, grid in ((4, GRID4), (2, (1, 2))):
