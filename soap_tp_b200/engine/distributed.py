@@ -520,22 +520,26 @@ def _product_with_basis(e: GridEngine, P: Tensor, Q: Tensor, work: Tensor, size:
 
 def estimated_order(P: Tensor, Q: Tensor, work: Tensor, size: int, block_size: int, grid) -> Tensor:
     e = engine_for(P.device, grid, block_size)
-    _product_with_basis(e, P, Q, work, size)
+    with TIMER.stage("refresh.power_iteration.product", P.device):
+        _product_with_basis(e, P, Q, work, size)
     lr, lc = e.rows_of(size), e.cols_of(size)
-    # partial column dots over my rows, one row of a (Pr x size) block-cyclic matrix with row blocks of 1
-    most_cols = numroc(size, e.nb, 0, e.Pc)
-    segment = e.comm.segment(f"estimates:{size}:{e.nb}", max(1, most_cols))
-    partial = segment.local[: max(1, lc)]
-    partial.zero_()
-    if lr and lc:
-        k.column_dot(Q, work, lr, lc, out=partial)
-    e.comm.barrier()
-    source = Source(segment, KIND_BLOCK_CYCLIC, e.Pr, size, 1, e.nb, e.Pr, e.Pc, e.world)
-    table = torch.empty((size, e.Pr), dtype=torch.float32, device=P.device).T   # Pr x size, column-major
-    dist_gather(source, IDENTITY, IDENTITY, e.Pr, size, out=table)
-    e.comm.barrier()
-    estimates = table.sum(dim=0)   # fixed order over Pr -> identical on every rank
-    return torch.argsort(estimates, descending=True, stable=True)
+    with TIMER.stage("refresh.power_iteration.estimates", P.device):
+        # partial column dots over my rows, one row of a (Pr x size) block-cyclic matrix with row blocks of 1
+        most_cols = numroc(size, e.nb, 0, e.Pc)
+        segment = e.comm.segment(f"estimates:{size}:{e.nb}", max(1, most_cols))
+        partial = segment.local[: max(1, lc)]
+        partial.zero_()
+        if lr and lc:
+            k.column_dot(Q, work, lr, lc, out=partial)
+        e.comm.barrier()
+        source = Source(segment, KIND_BLOCK_CYCLIC, e.Pr, size, 1, e.nb, e.Pr, e.Pc, e.world)
+        table = torch.empty((size, e.Pr), dtype=torch.float32, device=P.device).T   # Pr x size, column-major
+        dist_gather(source, IDENTITY, IDENTITY, e.Pr, size, out=table)
+        e.comm.barrier()
+    with TIMER.stage("refresh.power_iteration.sort", P.device):
+        estimates = table.sum(dim=0)   # fixed order over Pr -> identical on every rank
+        order = torch.argsort(estimates, descending=True, stable=True)
+    return order
 
 
 def _gather_dense(e: GridEngine, source: Source, size: int, column_order: Optional[Tensor] = None) -> Tensor:
@@ -754,7 +758,7 @@ def prepare_refresh(e: GridEngine, global_shape) -> None:
     e.packed_segment("middle", (cols, rows))
     from . import local
 
-    local.warm_refresh_kernels(e.device)
+    local.warm_refresh_kernels(e.device, sizes={rows, cols})
 
 
 def refresh(e: GridEngine, state: MutableMapping[str, Any], global_shape) -> Tuple[Tensor, Tensor]:

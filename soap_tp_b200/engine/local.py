@@ -175,15 +175,21 @@ def soap_step(
     return update
 
 
-_WARMED: Dict[str, bool] = {}
+_WARMED: Dict[Any, bool] = {}
 
 
-def warm_refresh_kernels(device) -> None:
+def warm_refresh_kernels(device, sizes=()) -> None:
     """Launch every kernel variant a refresh uses once, on a tiny problem.
 
     CUDA loads a kernel's code the first time it is launched; without this the first refresh of a
-    training run pays tens of milliseconds of module loading in the middle of a step.
+    training run pays tens of milliseconds of module loading in the middle of a step.  The library sort
+    picks its kernels by length, so the eigenvalue-order sort is warmed at the real ``sizes``.
     """
+    for size in sizes:
+        if not _WARMED.get((str(torch.device(device)), "sort", size)):
+            _WARMED[(str(torch.device(device)), "sort", size)] = True
+            table = torch.rand((size, 2), device=device).T
+            torch.argsort(table.sum(dim=0), descending=True, stable=True)
     key = str(torch.device(device))
     if _WARMED.get(key):
         return
@@ -197,6 +203,7 @@ def warm_refresh_kernels(device) -> None:
     from . import qr as qr_driver
 
     qr_driver.householder_qr_pair(factor_jobs)
+    qr_driver.householder_qr(matrix.clone(), out)      # a lone factorisation takes the forward-accumulation path
     estimated_order(matrix, out, torch.empty(n, n, device=device).T, n)
     k.gather2d(matrix, out, order, order)
     qr_driver.release_workspaces_for(n, device)
@@ -218,7 +225,7 @@ def prepare_refresh(rows: int, cols: int, device) -> None:
     workspace_matrix("perm", rows, cols, device)
     for tag, depth, width in (("X", rows, cols), ("U", rows, cols), ("T", cols, rows)):
         workspace_planes(tag, depth, width, device)
-    warm_refresh_kernels(device)
+    warm_refresh_kernels(device, sizes={rows, cols})
 
 
 def rotate(matrix: Tensor, Q_left: Tensor, Q_right: Tensor, global_shape, direction: str) -> Tensor:
