@@ -39,6 +39,7 @@ def main(argv=None) -> int:
     parser.add_argument("--rows", type=int, default=4096)
     parser.add_argument("--mode", default="store")
     parser.add_argument("--repeats", type=int, default=3)
+    parser.add_argument("--trace", action="store_true", help="panel: print clock64 stamps of one column step")
     args = parser.parse_args(argv)
 
     from ..engine import kernels as k
@@ -86,6 +87,22 @@ def main(argv=None) -> int:
                                        Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
                                        k.status_word(device).data_ptr(), k._stream())
             print(f"qr_panel rows={r}: {timed(fn, args.repeats):.1f} us/launch")
+            if args.trace:
+                # stamps taken by thread 0 of CTA 0 around column 64 (see the kernel); differences in SM cycles
+                stamps = torch.zeros(16, dtype=torch.int64, device=device)
+                k._C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, 128, v.hi.data_ptr(),
+                              v.lo.data_ptr(), v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, ws["tau"].data_ptr(),
+                              T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld,
+                              ws["exchange"].data_ptr(), k.status_word(device).data_ptr(), k._stream(),
+                              stamps.data_ptr(), 0)
+                torch.cuda.synchronize()
+                s = stamps.tolist()
+                order = [5, 7, 8, 1, 2, 3, 6, 0, 4]
+                names = ["loop top", "sweep 1 FMAs", "shuffles", "pivot row + publish", "T column (CTA 0)",
+                         "exchange", "barrier 1", "scalars + sweep 2 + barrier 2"]
+                print(f"column 64 of CTA 0: {s[4] - s[5]} cycles")
+                for a, b, name in zip(order[:-1], order[1:], names):
+                    print(f"  {name:32s} {s[b] - s[a]}")
         else:
             k.split_planes(rand(n, n), out=ws["V"])
             z, w = ws["V"].sub(0, 0, 128, n), ws["V"].sub(128, 0, 128, n - 128)
