@@ -9,9 +9,13 @@ identity, ``src/soap_tp/csrc/slate_bindings.cpp:125-189``).  Per 128-column pane
     W = V^T C_trailing             (split-K GEMM, partials summed in fixed order -> deterministic)
     C_trailing -= Z^T W            (GEMM whose epilogue read-modify-writes the operand planes)
 
-and the same three GEMMs in reverse panel order build the explicit ``Q`` from the identity.  The
+and the same three GEMMs build the explicit ``Q``: in reverse panel order from the identity when two
+factorisations run together (fewest flops), or forwards, panel by panel on a stream of its own under
+the panel chain, when a factorisation runs alone (nothing left to do after the last panel).  The
 trailing matrix and ``Q`` live as hi/lo operand planes throughout, so no separate split pass is
-needed between panels.  All arithmetic is fp32-class (3xTF32 products, fp32 panel).
+needed between panels.  Look-ahead: panel ``p + 1`` is factored on a high-priority stream as soon as
+the reflector of panel ``p`` has reached its columns, while the rest of the update proceeds.  All
+arithmetic is fp32-class (3xTF32 products, fp32 panel).
 """
 from __future__ import annotations
 
@@ -189,7 +193,7 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
         j0 = panels[p]
         bw, r = min(PANEL, n - j0), n - j0
         v = V.sub(j0, j0, r, bw)
-        z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else ws["Z_last"]
+        z = ws["Z"].sub(0, 0, bw, r)     # only full-width panels have columns to their right
         w = ws["W"].sub(0, 0, bw, count)
         block = C.sub(j0, first_col, r, count)
         _skinny_product(ws, v, block, w)                                                    # W = V^T C
@@ -238,9 +242,7 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
             vt, Tt = ws["Vt"][p], ws["Tt"][p]
             t_op = k.Planes(Tt.hi, Tt.lo, bw, bw, Tt.ld)
             vt_op = vt.sub(0, 0, bw, r)
-            if bw != PANEL:
-                ws["Z_last"] = k.Planes.empty(bw, r, device)
-            z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else ws["Z_last"]
+            z = ws["Z"].sub(0, 0, bw, r)
             k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z, force_narrow=True)            # Z = T V^T
             ahead = min(PANEL, nc)
             update(p, j0 + bw, ahead)
