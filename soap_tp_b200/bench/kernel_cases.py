@@ -39,6 +39,8 @@ def main(argv=None) -> int:
     parser.add_argument("--rows", type=int, default=4096)
     parser.add_argument("--mode", default="store")
     parser.add_argument("--repeats", type=int, default=3)
+    parser.add_argument("--pairs", action="store_true", help="panel: the two-columns-per-exchange kernel")
+    parser.add_argument("--rows-per-cta", type=int, default=256, choices=(128, 256), help="panel --pairs: CTA height")
     parser.add_argument("--trace", action="store_true", help="panel: print clock64 stamps of one column step")
     args = parser.parse_args(argv)
 
@@ -81,12 +83,22 @@ def main(argv=None) -> int:
         if args.case == "panel":
             r = args.rows
             panel, v, vt, T, Tt = ws["C"].sub(0, 0, r, 128), ws["V"].sub(0, 0, r, 128), ws["Vt"][0], ws["T"][0], ws["Tt"][0]
-            fn = lambda: k._C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, 128, v.hi.data_ptr(),
-                                       v.lo.data_ptr(), v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld,
-                                       ws["tau"].data_ptr(), T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(),
-                                       Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
-                                       k.status_word(device).data_ptr(), k._stream())
-            print(f"qr_panel rows={r}: {timed(fn, args.repeats):.1f} us/launch")
+            kernel = k._C.qr_panel_pairs if args.pairs else k._C.qr_panel
+            extra = (args.rows_per_cta,) if args.pairs else ()
+            fn = lambda: kernel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, 128, v.hi.data_ptr(),
+                                v.lo.data_ptr(), v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld,
+                                ws["tau"].data_ptr(), T.hi.data_ptr(), T.lo.data_ptr(), Tt.hi.data_ptr(),
+                                Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                                k.status_word(device).data_ptr(), k._stream(), *extra)
+            label = f"qr_panel_pairs ({args.rows_per_cta}-row CTAs)" if args.pairs else "qr_panel"
+            print(f"{label} rows={r}: {timed(fn, args.repeats):.1f} us/launch")
+            if args.pairs:
+                steps = torch.zeros(1, dtype=torch.int64, device=device)
+                kernel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, 128, v.hi.data_ptr(), v.lo.data_ptr(), v.ld,
+                       vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, ws["tau"].data_ptr(), T.hi.data_ptr(), T.lo.data_ptr(),
+                       Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                       k.status_word(device).data_ptr(), k._stream(), args.rows_per_cta, steps.data_ptr())
+                print(f"exchange steps for 128 columns: {int(steps.item())}")
             if args.trace:
                 # stamps taken by thread 0 of CTA 0 around column 64 (see the kernel); differences in SM cycles
                 stamps = torch.zeros(16, dtype=torch.int64, device=device)

@@ -130,6 +130,20 @@ PYBIND11_MODULE(_C, m) {
         py::arg("ldv"), py::arg("vt_hi"), py::arg("vt_lo"), py::arg("ldvt"), py::arg("tau"), py::arg("t_hi"),
         py::arg("t_lo"), py::arg("tt_hi"), py::arg("tt_lo"), py::arg("ldt"), py::arg("exchange"), py::arg("status"),
         py::arg("stream"), py::arg("trace") = 0, py::arg("debug_skip") = 0);
+  m.def("qr_panel_pairs",
+        [](uint64_t p_hi, uint64_t p_lo, int64_t ldp, int r, int b, uint64_t v_hi, uint64_t v_lo, int64_t ldv,
+           uint64_t vt_hi, uint64_t vt_lo, int64_t ldvt, uint64_t tau, uint64_t t_hi, uint64_t t_lo, uint64_t tt_hi,
+           uint64_t tt_lo, int64_t ldt, uint64_t exchange, uint64_t status, uint64_t stream, int rows_per_cta,
+           uint64_t steps_taken) {
+          qr_panel_pairs(ptr<const float>(p_hi), ptr<const float>(p_lo), ldp, r, b, ptr<float>(v_hi), ptr<float>(v_lo),
+                         ldv, ptr<float>(vt_hi), ptr<float>(vt_lo), ldvt, ptr<float>(tau), ptr<float>(t_hi),
+                         ptr<float>(t_lo), ptr<float>(tt_hi), ptr<float>(tt_lo), ldt, ptr<float>(exchange),
+                         ptr<int>(status), stream_of(stream), rows_per_cta, ptr<long long>(steps_taken));
+        },
+        py::arg("p_hi"), py::arg("p_lo"), py::arg("ldp"), py::arg("r"), py::arg("b"), py::arg("v_hi"), py::arg("v_lo"),
+        py::arg("ldv"), py::arg("vt_hi"), py::arg("vt_lo"), py::arg("ldvt"), py::arg("tau"), py::arg("t_hi"),
+        py::arg("t_lo"), py::arg("tt_hi"), py::arg("tt_lo"), py::arg("ldt"), py::arg("exchange"), py::arg("status"),
+        py::arg("stream"), py::arg("rows_per_cta") = 256, py::arg("steps_taken") = 0);
   m.def("sum_partials_to_planes",
         [](uint64_t partials, int splits, int64_t stride, int64_t ld, uint64_t hi, uint64_t lo, int64_t ldp, int rows,
            int cols, uint64_t stream) {

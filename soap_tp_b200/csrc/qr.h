@@ -22,6 +22,16 @@ void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, f
               int64_t ldt, float* exchange, int* status, cudaStream_t stream, long long* trace = nullptr,
               int debug_skip = 0);
 
+// Same contract, two Householder columns per exchange step where that is numerically safe (see
+// qr_panel_pairs.cu).  `rows_per_cta` is 256 (fewest SMs) or 128 (fastest: twice the CTAs, half the registers
+// per thread taken by the slab); the grid is ceil(r / rows_per_cta) CTAs.  `exchange` must hold at least
+// 8 * (gridsize + 1) * 128 floats, 16-byte aligned.  `steps_taken` (optional, device) receives the number of
+// exchange steps the panel needed (b / 2 when every step retired two columns).
+void qr_panel_pairs(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, float* v_hi, float* v_lo, int64_t ldv,
+                    float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* t_hi, float* t_lo, float* tt_hi,
+                    float* tt_lo, int64_t ldt, float* exchange, int* status, cudaStream_t stream,
+                    int rows_per_cta = 256, long long* steps_taken = nullptr);
+
 // planes <- sum over `splits` partial matrices (rows x cols, column-major pitch ld, `stride` floats apart).
 void sum_partials_to_planes(const float* partials, int splits, int64_t stride, int64_t ld, float* hi, float* lo,
                             int64_t ldp, int rows, int cols, cudaStream_t stream);

@@ -29,6 +29,9 @@ from . import kernels as k
 
 _C = k._C
 PANEL = _C.QR_PANEL_WIDTH
+# Two Householder columns per exchange step of the panel kernel where that is numerically safe
+# (SOAP_TP_QR_PAIR_STEPS=0: the one-column kernel).
+PAIR_STEPS = os.environ.get("SOAP_TP_QR_PAIR_STEPS", "1") != "0"
 _WORKSPACES: Dict[tuple, dict] = {}
 
 
@@ -48,7 +51,7 @@ def _workspace(n: int, device, slot: int = 0) -> dict:
             "W": k.Planes.empty(PANEL, n, device),
             "tau": torch.zeros(n + PANEL, dtype=torch.float32, device=device),
             "S": torch.zeros(PANEL * PANEL, dtype=torch.float32, device=device),
-            "exchange": torch.zeros(4 * 160 * PANEL + 4 * PANEL, dtype=torch.float32, device=device),
+            "exchange": torch.zeros(8 * 160 * PANEL + 8 * PANEL, dtype=torch.float32, device=device),
             "partials": torch.empty(16 * PANEL * n, dtype=torch.float32, device=device),
             "partials_q": None, "Zq": None, "Wq": None,    # forward accumulation of Q (allocated on first use)
             "staging": torch.empty((n, n), dtype=torch.float32, device=device).T,
@@ -179,10 +182,16 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
         T, Tt = ws["T"][p], ws["Tt"][p]
         side.wait_event(after)
         with torch.cuda.stream(side):
-            _C.qr_panel(panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(),
-                        v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(),
-                        T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
-                        k.status_word(device).data_ptr(), stream())
+            arguments = (panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(),
+                         v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(),
+                         T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                         k.status_word(device).data_ptr(), stream())
+            if PAIR_STEPS:
+                # 128-row CTAs sweep their slabs faster (fewer registers held by the slab, more loads in flight) but
+                # double the words every CTA polls: measured 344 vs 460 us at 2048 rows, 529 vs 464 us at 8192 rows
+                _C.qr_panel_pairs(*arguments, 128 if r <= 4096 else 256)
+            else:
+                _C.qr_panel(*arguments)
             k._count("qr_panel_kernel")
             done = torch.cuda.Event()
             done.record(side)
