@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_pairs_kernel(PanelA
   constexpr int kCtaRows = 4 * kPer;
   constexpr int kSlice = kPer + 4;     // floats between the four slices of a pivot column in shared memory
   constexpr int kVec = kPer / 4;       // 128-bit loads per sweep and pivot column
-  constexpr int kPollPairs = kPer == 64 ? 9 : 17;   // 128-bit loads a thread keeps in flight per polling round
+  constexpr int kPollPairs = kPer == 64 ? 7 : 17;   // 128-bit loads a thread keeps in flight per polling round
   __shared__ __align__(16) float xcol[2][4 * kSlice];   // pivot column c (double buffered); zero above the pivot row
   __shared__ __align__(16) float ycol[2][4 * kSlice];   // column c + 1 as it is before H_c is applied
   __shared__ float stats[2][8];                         // {p1_c, D1_c, p2_c, -, p1_c1, D1_c1, p2_c1, D2_c1}
