@@ -187,9 +187,8 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
                          T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
                          k.status_word(device).data_ptr(), stream())
             if PAIR_STEPS:
-                # 128-row CTAs sweep their slabs faster (fewer registers held by the slab, more loads in flight) but
-                # double the words every CTA polls: measured 344 vs 460 us at 2048 rows, 529 vs 464 us at 8192 rows
-                _C.qr_panel_pairs(*arguments, 128 if r <= 4096 else 256)
+                # 256-row CTAs: measured faster than (2048 rows and up) or within 2 % of (1024 rows) 128-row CTAs
+                _C.qr_panel_pairs(*arguments, 256)
             else:
                 _C.qr_panel(*arguments)
             k._count("qr_panel_kernel")

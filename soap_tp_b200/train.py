@@ -85,7 +85,7 @@ def train(args: argparse.Namespace) -> dict:
             torch.cuda.synchronize()
         elapsed = torch.tensor([time.perf_counter() - start], dtype=torch.float64, device=device)
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         seconds.append(float(elapsed))
         emit_timing("step", step=step, seconds=seconds[-1], loss=losses[-1],
                     tokens_per_second=args.global_batch * seq_len / seconds[-1])
