@@ -360,8 +360,8 @@ def main() -> int:
     args = parse_args()
     if args.impl == "reference" and not (ROOT / "baseline" / "_ref" / "soap_tp").exists():
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed "
-                          "(python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse "
-                          "--target baseline/_ref /root/reference)"}), flush=True)
+                          "(python -m pip install --no-index --no-build-isolation --target baseline/_ref "
+                          "<checkout of the reference>)"}), flush=True)
         return 0
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         return relaunch_under_torchrun(args)
