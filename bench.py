@@ -211,7 +211,7 @@ def run(args: argparse.Namespace) -> int:
     # so it runs ONE loop (the end-to-end one below) and takes both numbers from it: CUDA events around that
     # loop give the device time (the prefetched copy and the 4-byte read-back are under 1 % of its step).
     single_loop = args.impl == "reference"
-    budget_seconds = float(os.environ.get("SOAP_TP_REFERENCE_BUDGET_SECONDS", "2700"))
+    budget_seconds = float(os.environ.get("SOAP_TP_REFERENCE_BUDGET_SECONDS", "1200"))
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
