@@ -251,7 +251,11 @@ def run(args: argparse.Namespace) -> int:
     arrived = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     used = [False, False]
-    metric_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    # the step's metric comes back into pinned memory every step; the host reads it one step later, as a
+    # training loop that logs its loss without stalling the device does
+    metric_host = torch.empty(2, dtype=torch.float32).pin_memory()
+    metric_ready = [torch.cuda.Event() for _ in range(2)]
+    metrics_read = []
 
     def prefetch(index: int) -> None:
         slot = index % 2
@@ -275,8 +279,11 @@ def run(args: argparse.Namespace) -> int:
         update = step_fn(device_buffers[slot])
         consumed[slot].record()
         used[slot] = True
-        metric_host.copy_(torch.linalg.vector_norm(update).reshape(1), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        metric_host[slot:slot + 1].copy_(torch.linalg.vector_norm(update).reshape(1), non_blocking=True)
+        metric_ready[slot].record()
+        if i > 0:
+            metric_ready[1 - slot].synchronize()
+            metrics_read.append(float(metric_host[1 - slot]))
         steps_done += 1
         if single_loop:
             # every rank must take the same decision: agree on the slowest rank's clock
@@ -285,6 +292,9 @@ def run(args: argparse.Namespace) -> int:
             if float(elapsed.item()) > budget_seconds and steps_done < args.steps:
                 break
     loop_stop.record()
+    if steps_done:
+        metric_ready[(steps_done - 1) % 2].synchronize()
+        metrics_read.append(float(metric_host[(steps_done - 1) % 2]))
     fence()
     e2e_ms = torch.tensor([(time.perf_counter() - e2e_start) * 1e3], dtype=torch.float64, device=device)
     dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
