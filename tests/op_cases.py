@@ -321,3 +321,27 @@ def case_gram_1d(rank, world, device_kind, shape, beta):
     assert relative_l2(R.cpu().double(), eR) < 1e-5
     fresh = update_left_preconditioner_from_col_shards(shard, None, 0.0)
     assert relative_l2(fresh.cpu().double(), (fd @ fd.T)[rank * rows_here:(rank + 1) * rows_here]) < 1e-5
+
+
+def case_gram_1d_subgroups(rank, world, device_kind, shape, beta):
+    """The 1-D Gram updates over a sub-group: two independent tensor-parallel groups of half the world."""
+    from soap_tp_b200.ops.gram_1d import (update_left_preconditioner_from_col_shards,
+                                          update_right_preconditioner_from_col_shards)
+
+    assert world % 2 == 0
+    half = world // 2
+    groups = [dist.new_group(list(range(g * half, (g + 1) * half))) for g in range(2)]
+    mine = rank // half
+    group, local_rank = groups[mine], rank % half
+    device = dev(device_kind, rank)
+    rows, cols = shape
+    full = seeded(shape, 31 + mine)                      # each group has its own gradient
+    shard = full.chunk(half, dim=1)[local_rank].contiguous().to(device)
+    rows_here, cols_here = rows // half, cols // half
+    L = update_left_preconditioner_from_col_shards(shard, None, beta, TP_group=group)
+    R = update_right_preconditioner_from_col_shards(shard, None, beta, TP_group=group)
+    fd = full.double()
+    eL = ((1 - beta) * fd @ fd.T)[local_rank * rows_here:(local_rank + 1) * rows_here]
+    eR = ((1 - beta) * fd.T @ fd)[local_rank * cols_here:(local_rank + 1) * cols_here]
+    assert L.shape == (rows_here, rows) and R.shape == (cols_here, cols)
+    assert relative_l2(L.cpu().double(), eL) < 1e-5 and relative_l2(R.cpu().double(), eR) < 1e-5

@@ -27,6 +27,7 @@ def test_gram_updates():
     specs = [("case_gram", (shape, 2, GRID, sd, 0.0)) for shape in RECT for sd in (0, 1)]
     specs.append(("case_gram", ((9, 13), 2, GRID, 1, 0.25)))      # beta and initial value
     specs += [("case_gram_1d", ((8, 12), 0.0)), ("case_gram_1d", ((12, 8), 0.25))]   # 1-D row-sharded results
+    specs += [("case_gram_1d_subgroups", ((8, 12), 0.25))]
     run_distributed(cases.case_batch, 4, "cpu", specs)
 
 
