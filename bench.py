@@ -10,13 +10,19 @@ most-square process grid ((1,1), (1,2), (2,2), (2,4)), gradients i.i.d. N(0, 1) 
 step, betas (0.95, 0.95), basis refresh every 10 steps.  STRONG scaling: the parameter is fixed
 while N grows.  The first call (basis initialisation) is part of the warm-up.
 
-Two measurements are reported in one JSON line on rank 0:
+Reported in one JSON line on rank 0:
 
 * ``value``  -- device time of K ``soap_step`` calls whose gradients are resident on the GPU
   (CUDA events, barrier + synchronise on both sides, maximum over ranks) / K;
 * ``e2e``    -- the same K calls through the public API where every step first copies its gradient
   shard from pinned host memory to the device and ends with a device-to-host read of the update
-  norm (host wall clock around barrier + synchronise, maximum over ranks) / K.
+  norm (host wall clock around barrier + synchronise, maximum over ranks) / K;
+* ``median_steady_ms``, ``refresh_step_ms``, ``init_ms`` -- from one CUDA-event pair per step (maximum over
+  ranks per step): the median step without a refresh, the mean step with one, and the first call (both
+  eigenbases), which is outside the timed region;
+* ``check`` -- correctness figures computed after the timed region (``--no-check`` skips them): orthogonality
+  of both bases, both Gram matrices against a float64 EMA of the same gradient sequence, and a 2048 x 2048
+  side problem on the same grid against the single-GPU pipeline (``soap_tp_b200/bench/checks.py``).
 
 For N > 1 the script expects one process per GPU (``python -m torch.distributed.run
 --nproc-per-node N ...``); started without that environment it re-launches itself that way.
@@ -51,6 +57,9 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--refresh-interval", type=int, default=REFRESH)
     parser.add_argument("--basis-implementation", default=None)
     parser.add_argument("--stage-timing", action="store_true", help="also print per-stage device times (stderr)")
+    parser.add_argument("--check", dest="check", action="store_true", default=True,
+                        help="after the timed region, report correctness figures of the state it left (default)")
+    parser.add_argument("--no-check", dest="check", action="store_false")
     args = parser.parse_args()
     if args.warmup < 1:
         parser.error("--warmup must be at least 1 (the first call initialises the bases)")
@@ -177,10 +186,12 @@ def run(args: argparse.Namespace) -> int:
         basis = args.basis_implementation or "jacobi"
         state: dict = {}
 
-        def step_fn(gradient):
-            return soap_step(gradient, state, global_shape=(size, size), shard_dim=args.shard_dim,
-                             block_size=args.block_size, process_grid_shape=grid,
-                             basis_refresh_interval=args.refresh_interval, basis_implementation=basis)
+        def make_step(side: int, target: dict):
+            return lambda gradient: soap_step(
+                gradient, target, global_shape=(side, side), shard_dim=args.shard_dim, block_size=args.block_size,
+                process_grid_shape=grid, basis_refresh_interval=args.refresh_interval, basis_implementation=basis)
+
+        step_fn = make_step(size, state)
 
         launches = kernels.total_launches
         if args.stage_timing:
@@ -195,15 +206,39 @@ def run(args: argparse.Namespace) -> int:
     cache: dict = {}
     pool = 4  # distinct resident gradients cycled through the timed region
     counter = 0
+    history: list[int] = []      # gradient index of every call so far (for the checks after the timed region)
+
+    def max_over_ranks(values) -> list[float]:
+        tensor = torch.tensor(list(values), dtype=torch.float64, device=device)
+        dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+        return [float(v) for v in tensor.tolist()]
+
+    def step_summary(per_step_ms: list[float], first_call_index: int) -> dict:
+        """Median of the steps without a refresh and mean of those with one (call c refreshes when c % interval == 0)."""
+        steady = [t for i, t in enumerate(per_step_ms) if (first_call_index + i) % args.refresh_interval]
+        refresh = [t for i, t in enumerate(per_step_ms) if (first_call_index + i) % args.refresh_interval == 0]
+        return {
+            "median_steady_ms": round(statistics.median(steady), 4) if steady else None,
+            "refresh_step_ms": round(sum(refresh) / len(refresh), 4) if refresh else None,
+            "refresh_steps_timed": len(refresh),
+            "step_ms": [round(t, 3) for t in per_step_ms],
+        }
 
     # ---- warm-up (first call = basis initialisation) ----
     init_start = time.perf_counter()
+    init_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     for _ in range(args.warmup):
+        if counter == 0:
+            fence()
+            init_events[0].record()
         step_fn(gradient_for(counter, rank, shard_shape, device, cache))
+        history.append(counter)
         counter += 1
         if counter == 1:
+            init_events[1].record()
             fence()
             init_seconds = time.perf_counter() - init_start
+            init_ms = max_over_ranks([init_events[0].elapsed_time(init_events[1])])[0]
     fence()
 
     # ---- device-timed region ----
@@ -221,15 +256,18 @@ def run(args: argparse.Namespace) -> int:
         if args.impl == "ours" and args.stage_timing:
             GLOBAL_STAGE_TIMER.reset()
         resident = [gradient_for(counter + i, rank, shard_shape, device, cache) for i in range(pool)]
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         fence()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
+        marks[0].record()
         for i in range(args.steps):
             step_fn(resident[i % pool])
-        stop.record()
+            marks[i + 1].record()
         fence()
-        device_ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+        history.extend(counter + i % pool for i in range(args.steps))
+        device_ms = torch.tensor([marks[0].elapsed_time(marks[-1])], dtype=torch.float64, device=device)
         dist.all_reduce(device_ms, op=dist.ReduceOp.MAX)
+        per_step = max_over_ranks(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
+        summary = step_summary(per_step, len(history) - args.steps)
         launches_timed = launches() - launches_before
         if args.impl == "ours" and args.stage_timing:
             stages = GLOBAL_STAGE_TIMER.summary()
@@ -267,8 +305,11 @@ def run(args: argparse.Namespace) -> int:
 
     fence()
     loop_start, loop_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    loop_marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    e2e_first_call = len(history)
     e2e_start = time.perf_counter()
     loop_start.record()
+    loop_marks[0].record()
     prefetch(0)
     steps_done = 0
     for i in range(args.steps):
@@ -285,6 +326,8 @@ def run(args: argparse.Namespace) -> int:
             metric_ready[1 - slot].synchronize()
             metrics_read.append(float(metric_host[1 - slot]))
         steps_done += 1
+        loop_marks[steps_done].record()
+        history.append(counter + i % pool)
         if single_loop:
             # every rank must take the same decision: agree on the slowest rank's clock
             elapsed = torch.tensor([time.perf_counter() - e2e_start], dtype=torch.float64, device=device)
@@ -303,6 +346,8 @@ def run(args: argparse.Namespace) -> int:
         dist.all_reduce(device_ms, op=dist.ReduceOp.MAX)
         launches_timed = launches() - launches_before
         clocks = sampler.stop() if rank == 0 else {}
+        per_step = max_over_ranks(loop_marks[i].elapsed_time(loop_marks[i + 1]) for i in range(steps_done))
+        summary = step_summary(per_step, e2e_first_call)
         if steps_done < args.steps:
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable":
@@ -313,12 +358,35 @@ def run(args: argparse.Namespace) -> int:
             dist.destroy_process_group()
             return 0
 
+    check: dict | None = None
     if args.impl == "ours":
         from soap_tp_b200.engine import kernels
 
         kernels.check_status()
         if args.stage_timing and rank == 0:
             print(json.dumps({"launch_counts": kernels.LAUNCH_COUNTS}), file=sys.stderr)
+        if args.check:
+            from soap_tp_b200.bench import checks
+
+            def full_gradient(index: int):
+                shards = [gradient_for(index, r, shard_shape, device, cache) for r in range(world)]
+                return shards[0] if world == 1 else torch.cat(shards, dim=args.shard_dim)
+
+            check = {
+                "left_basis_max_abs_QtQ_minus_I": checks.basis_orthogonality(state["left_basis"], size, args.block_size, grid),
+                "right_basis_max_abs_QtQ_minus_I": checks.basis_orthogonality(state["right_basis"], size, args.block_size, grid),
+                "gram_relative_error_vs_float64": checks.gram_error(state, full_gradient, history, (size, size),
+                                                                    args.block_size, grid, 0.95),
+                "steps_behind_the_state": len(history),
+            }
+            side = min(2048, size)
+            if world > 1 and side % world == 0:
+                check["side_problem_vs_single_gpu_pipeline"] = checks.side_problem_against_one_gpu(
+                    lambda: make_step(side, {}), side, args.block_size, grid, args.shard_dim,
+                    steps=args.refresh_interval + 2, interval=args.refresh_interval)
+            else:
+                check["side_problem_vs_single_gpu_pipeline"] = None    # one rank: the two paths are the same code
+            kernels.check_status()
 
     ms_per_step = float(device_ms.item()) / args.steps
     e2e_per_step = float(e2e_ms.item()) / args.steps
@@ -345,13 +413,19 @@ def run(args: argparse.Namespace) -> int:
                 "parallelism": f"tp{world} column shards, 2-D block-cyclic grid {grid[0]}x{grid[1]}, block {args.block_size}",
                 "shard_dim": args.shard_dim,
                 "basis_refresh_interval": args.refresh_interval,
-                "basis_implementation": basis,
                 "l2": "no flush: each step streams > 1 GiB of operand planes and state per GPU (L2 is 126 MB); "
                       f"{pool} distinct resident gradients are cycled",
+            },
+            # per-arm facts, kept out of `config` so that both arms print the same workload description
+            "run_info": {
+                "basis_implementation": basis,
                 "initialization_seconds": round(init_seconds, 3),
                 "timed_loop": ("one loop: device events around the end-to-end loop" if single_loop
                                else "device loop on resident gradients, then a separate end-to-end loop"),
             },
+            "init_ms": round(init_ms, 2),
+            **summary,
+            "check": check,
             "clocks": clocks,
             "e2e": {
                 "value": round(e2e_per_step, 4),

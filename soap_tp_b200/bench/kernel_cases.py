@@ -41,7 +41,8 @@ def main(argv=None) -> int:
     parser.add_argument("--repeats", type=int, default=3)
     parser.add_argument("--pairs", action="store_true", help="panel: the two-columns-per-exchange kernel")
     parser.add_argument("--rows-per-cta", type=int, default=256, choices=(128, 256), help="panel --pairs: CTA height")
-    parser.add_argument("--trace", action="store_true", help="panel: print clock64 stamps of one column step")
+    parser.add_argument("--trace", action="store_true",
+                        help="panel: print clock64 stamps of one column step (needs a library built with SOAP_QR_TRACE=1)")
     args = parser.parse_args(argv)
 
     from ..engine import kernels as k

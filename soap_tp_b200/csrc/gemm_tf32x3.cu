@@ -30,6 +30,7 @@
 #include <tuple>
 
 #include "gemm.h"
+#include "launch_util.h"
 #include "ptx.cuh"
 
 namespace soapb200 {
@@ -540,13 +541,8 @@ CUtensorMap make_operand_map(const float* base, int64_t K, int64_t rows, int64_t
 template <int BN, int MODE>
 void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
   using Cfg = TileConfig<BN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           Cfg::kSmemBytes);
-    if (err != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(err));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(gemm_tf32x3_kernel<BN, MODE>), Cfg::kSmemBytes, configured, "gemm_tf32x3");
   GemmMaps maps;
   const int64_t a_k = ops.a_k_total ? ops.a_k_total : prob.K, a_rows = ops.a_rows_total ? ops.a_rows_total : prob.M;
   const int64_t b_k = ops.b_k_total ? ops.b_k_total : prob.K, b_rows = ops.b_rows_total ? ops.b_rows_total : prob.N;

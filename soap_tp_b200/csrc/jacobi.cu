@@ -14,6 +14,7 @@
 #include <string>
 
 #include "jacobi.h"
+#include "launch_util.h"
 
 namespace soapb200 {
 namespace {
@@ -154,12 +155,8 @@ void jacobi_small(const float* s_hi, const float* s_lo, int64_t lds, int batches
                   float* offdiag, float scale, int max_sweeps, float tolerance, cudaStream_t stream) {
   if (batches <= 0) return;
   const size_t smem = (2 * static_cast<size_t>(kN) * kPitch + 4) * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(jacobi_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) throw std::runtime_error(std::string("jacobi_small attribute: ") + cudaGetErrorString(err));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(jacobi_small_kernel), smem, configured, "jacobi_small");
   jacobi_small_kernel<<<batches, kThreads, smem, stream>>>(s_hi, s_lo, lds, u_hi, u_lo, ldu, offdiag, scale, max_sweeps,
                                                          tolerance);
   cudaError_t err = cudaGetLastError();

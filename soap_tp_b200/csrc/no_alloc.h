@@ -20,7 +20,9 @@
 //     kernels can run at the same time on one GPU (different streams, no ordering) would trample each
 //     other's exchange words -- order them;
 //   * the first call on each device looks up the array's device address.  Make that first call
-//     outside any stream capture.
+//     outside any stream capture, and from one host thread: the per-device table of looked-up addresses
+//     is not protected by a lock, so two threads that both make the FIRST call for a device race on it
+//     (later calls only read the table);
 //   * no cudaMalloc, cudaFree or other allocating routine is called, here or in what it calls.
 #pragma once
 

@@ -10,17 +10,9 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
-namespace soapb200 {
+#include "status.h"
 
-// ---- status codes written to the device status word ------------------------------------------
-enum StatusCode : int {
-  kStatusOk = 0,
-  kStatusTmaWaitTimeout = 1,     // consumer never saw a full stage
-  kStatusSlotWaitTimeout = 2,    // producer never got an empty stage back
-  kStatusAccumWaitTimeout = 3,   // epilogue never saw the accumulator commit
-  kStatusBarrierTimeout = 4,     // cross-rank barrier flag never arrived
-  kStatusBadArgument = 5,
-};
+namespace soapb200 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -33,6 +33,17 @@ inline void check_launch(const char* what) {
 }
 
 
+// Diagnostics that the default build leaves out: clock64 stamps of one column step of CTA 0 and switches that
+// skip parts of the step (compile with -DSOAP_QR_TRACE; `kernel_cases panel --trace` needs such a build).
+#ifdef SOAP_QR_TRACE
+#define QR_STAMP(when, index) \
+  do { if (a.trace && blockIdx.x == 0 && t == 0 && (when)) a.trace[(index)] = clock64(); } while (0)
+#define QR_SKIP(bit) ((a.debug_skip & (bit)) != 0)
+#else
+#define QR_STAMP(when, index) do { } while (0)
+#define QR_SKIP(bit) false
+#endif
+
 constexpr int kMaxPollWords = 10;   // words one thread requests per polling round (40 CTAs' worth per round)
 
 constexpr int kSlice = 64 + 4;   // floats between the four 64-row slices of the pivot column in shared memory
@@ -96,7 +107,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
     unsigned long long* slots = a.exchange + static_cast<int64_t>(parity) * (ctas + 1) * kB;
     const int pivot_local = c - row0;                   // local index of the pivot row (may be outside this CTA)
     const bool pivot_mine = pivot_local >= my_first && pivot_local < my_first + 64;
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[7] = clock64();
+    QR_STAMP(c == 64, 7);
     // ---- sweep 1: dot product of the pivot column with this lane's slice of column j ----
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
     {
@@ -111,20 +122,20 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
       }
     }
     float partial = (acc0 + acc1) + (acc2 + acc3);
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[8] = clock64();
+    QR_STAMP(c == 64, 8);
     partial += __shfl_xor_sync(0xffffffffu, partial, 1);
     partial += __shfl_xor_sync(0xffffffffu, partial, 2);     // all four lanes: this CTA's partial dot for column j
     float row_value = 0.f;                                    // entry (c, j) of the panel, on the lane that holds it
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[1] = clock64();
-    if (pivot_mine && !(a.debug_skip & 2)) row_value = take_pivot_entry(P, pivot_local - my_first, false);
+    QR_STAMP(c == 64, 1);
+    if (pivot_mine && !QR_SKIP(2)) row_value = take_pivot_entry(P, pivot_local - my_first, false);
     if (ctas > 1) {
       if (q == 0) ll_publish(&slots[static_cast<int64_t>(blockIdx.x) * kB + j], partial, seq);
       if (pivot_mine) ll_publish(&slots[static_cast<int64_t>(ctas) * kB + j], row_value, seq);
     }
     // ---- CTA 0, while the published words travel: column c-1 of T (four threads per row) ----
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[2] = clock64();
-    if (blockIdx.x == 0 && c > 0 && !(a.debug_skip & 1)) t_column(T, scol, taus, c - 1, t);
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[3] = clock64();
+    QR_STAMP(c == 64, 2);
+    if (blockIdx.x == 0 && c > 0 && !QR_SKIP(1)) t_column(T, scol, taus, c - 1, t);
+    QR_STAMP(c == 64, 3);
     // ---- exchange: lane q polls the words of CTAs q, q+4, q+8, ... (index `ctas` = the pivot row) ----
     float total = partial, prow = row_value;
     if (ctas > 1) {
@@ -159,7 +170,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
       }
       if (failed) {
         abort_flag = 1;
-        atomicCAS(a.status, 0, 4);
+        atomicCAS(a.status, 0, kStatusPanelExchangeTimeout);
       }
       // fixed-shape reduction over the four lanes: identical on every CTA
       const float p1 = __shfl_xor_sync(0xffffffffu, part, 1);
@@ -176,9 +187,9 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
       pivot_stats[parity][1] = total;
     }
     if (ctas == 1 && j == c && q == 0) pivot_stats[parity][1] = total;
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[6] = clock64();
+    QR_STAMP(c == 64, 6);
     __syncthreads();                                                              // barrier 1
-    if (a.trace && blockIdx.x == 0 && t == 0 && c == 64) a.trace[0] = clock64();
+    QR_STAMP(c == 64, 0);
     if (abort_flag) break;
     if (ctas == 1) prow = pivot_row_local[j];
     // finished columns are kept unscaled in the registers: apply their scale to the two dot-like values
@@ -218,7 +229,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
       }
       // Row c right of the pivot now only holds R entries nobody reads again: zero them so that later
       // pivot columns leave the registers already masked above their pivot row.
-      if (pivot_mine && !(a.debug_skip & 2)) take_pivot_entry(P, pivot_local - my_first, true);
+      if (pivot_mine && !QR_SKIP(2)) take_pivot_entry(P, pivot_local - my_first, true);
       if (j == c + 1) {
         float4* x4 = reinterpret_cast<float4*>(&xcol[parity ^ 1][q * kSlice]);
 #pragma unroll
@@ -226,7 +237,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_kernel(PanelArgs a)
       }
     }
     __syncthreads();                                                              // barrier 2
-    if (a.trace && blockIdx.x == 0 && t == 0 && (c == 64 || c == 63)) a.trace[c == 64 ? 4 : 5] = clock64();
+    QR_STAMP(c == 64 || c == 63, c == 64 ? 4 : 5);
   }
 
   // ---- CTA 0: last column of T, then T and T^T as operand planes ----
@@ -325,22 +336,23 @@ inline int grid_for(int64_t total) {
 
 }  // namespace
 
+unsigned int next_panel_epoch() {
+  static unsigned int epoch = 0;
+  epoch = (epoch + 1) & 0xFFFFFFu;
+  if (epoch == 0) epoch = 1;
+  return epoch;
+}
+
 void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, float* v_hi, float* v_lo, int64_t ldv,
               float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* t_hi, float* t_lo, float* tt_hi, float* tt_lo,
               int64_t ldt, float* exchange, int* status, cudaStream_t stream, long long* trace, int debug_skip) {
   if (r <= 0 || b <= 0) return;
   if (b > kB) throw std::invalid_argument("qr_panel: panel wider than 128 columns");
   if (r > kQrMaxRows) throw std::invalid_argument("qr_panel: more rows than one cooperative grid can hold");
-  static unsigned int epoch = 0;
-  epoch = (epoch + 1) & 0xFFFFFFu;
-  if (epoch == 0) epoch = 1;
+  const unsigned int epoch = next_panel_epoch();
   const size_t smem = static_cast<size_t>(kB) * kPitch * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t attr = cudaFuncSetAttribute(qr_panel_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (attr != cudaSuccess) throw std::runtime_error(std::string("qr_panel attribute: ") + cudaGetErrorString(attr));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(qr_panel_kernel), smem, configured, "qr_panel");
   PanelArgs args{p_hi, p_lo, ldp, r, b, v_hi, v_lo, ldv, vt_hi, vt_lo, ldvt, tau, t_hi, t_lo, tt_hi, tt_lo, ldt,
                  reinterpret_cast<unsigned long long*>(exchange), epoch, status, trace, debug_skip};
   void* params[] = {&args};

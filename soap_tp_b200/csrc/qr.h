@@ -16,7 +16,8 @@ constexpr int kQrMaxRows = 148 * kQrRowsPerCta;  // one CTA per SM at most (coop
 // H_0 ... H_{b-1} = I - V T V^T in both orientations (T and T^T, b x b, pitch ldt).
 // `exchange` is 8-byte-aligned scratch of at least 4 * (gridsize + 1) * 128 floats that persists
 // between calls; `status` is the device status word a timed-out exchange reports to.  Cooperative
-// launch of ceil(r / 256) CTAs.  `trace` (optional, 6 x int64) receives clock64 stamps of one column step.
+// launch of ceil(r / 256) CTAs.  `trace` (optional, 16 x int64) receives clock64 stamps of one column step and
+// `debug_skip` switches parts of the step off, both only in a build with -DSOAP_QR_TRACE.
 void qr_panel(const float* p_hi, const float* p_lo, int64_t ldp, int r, int b, float* v_hi, float* v_lo, int64_t ldv,
               float* vt_hi, float* vt_lo, int64_t ldvt, float* tau, float* t_hi, float* t_lo, float* tt_hi, float* tt_lo,
               int64_t ldt, float* exchange, int* status, cudaStream_t stream, long long* trace = nullptr,

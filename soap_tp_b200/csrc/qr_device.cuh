@@ -3,9 +3,17 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include "launch_util.h"
 #include "qr.h"
+#include "status.h"
 
 namespace soapb200 {
+
+// Sequence base of the next panel launch.  One counter for both panel kernels: they may be handed the
+// same exchange buffer with different slot layouts, and a sequence number used by one must never be
+// accepted by the other on a stale word.
+unsigned int next_panel_epoch();
+
 namespace qrdev {
 
 constexpr int kB = kQrPanelWidth;
@@ -41,8 +49,10 @@ struct PanelArgs {
   unsigned long long* exchange;  // [2][ctas + 1][kB] packed {value, sequence} words
   unsigned int epoch;            // distinguishes this launch's words from stale ones in `exchange`
   int* status;
-  long long* trace;              // optional: clock64 stamps of CTA 0 at column 64 (diagnostics), may be null
-  int debug_skip;                // diagnostics only: bit 0 skips the T column, bit 1 the pivot-row bookkeeping
+  long long* trace;              // optional diagnostics output, may be null: the pair kernel stores its number of
+                                 // exchange steps; the one-column kernel stores clock64 stamps of CTA 0 at column 64
+                                 // when it is compiled with SOAP_QR_TRACE
+  int debug_skip;                // SOAP_QR_TRACE builds only: bit 0 skips the T column, bit 1 the pivot-row bookkeeping
 };
 
 // One 64-bit word carries a value and the sequence number that says which step it belongs to, so a

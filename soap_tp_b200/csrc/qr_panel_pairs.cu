@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) qr_panel_pairs_kernel(PanelA
       }
       if (failed) {
         abort_flag = 1;
-        atomicCAS(a.status, 0, 4);
+        atomicCAS(a.status, 0, kStatusPanelExchangeTimeout);
       }
       // fixed-shape reductions over the four lanes: identical on every CTA
       float o = __shfl_xor_sync(0xffffffffu, part1, 1);
@@ -467,13 +467,8 @@ namespace {
 template <int kPer>
 void launch_pairs(PanelArgs args, int r, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(kB) * kPitch * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t attr = cudaFuncSetAttribute(qr_panel_pairs_kernel<kPer>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(smem));
-    if (attr != cudaSuccess) throw std::runtime_error(std::string("qr_panel_pairs attribute: ") + cudaGetErrorString(attr));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(qr_panel_pairs_kernel<kPer>), smem, configured, "qr_panel_pairs");
   void* params[] = {&args};
   int ctas = (r + 4 * kPer - 1) / (4 * kPer);
   if (ctas > 1 && ctas < 148) ++ctas;   // the rowless CTA that builds T (see the kernel)
@@ -495,9 +490,7 @@ void qr_panel_pairs(const float* p_hi, const float* p_lo, int64_t ldp, int r, in
   if (r > kQrMaxRows) throw std::invalid_argument("qr_panel_pairs: more rows than one cooperative grid can hold");
   if (rows_per_cta != 128 && rows_per_cta != 256) throw std::invalid_argument("qr_panel_pairs: rows_per_cta is 128 or 256");
   if (rows_per_cta == 128 && r > 148 * 128) rows_per_cta = 256;   // one CTA per SM at most
-  static unsigned int epoch = 0;
-  epoch = (epoch + 1) & 0xFFFFFFu;
-  if (epoch == 0) epoch = 1;
+  const unsigned int epoch = next_panel_epoch();
   PanelArgs args{p_hi, p_lo, ldp, r, b, v_hi, v_lo, ldv, vt_hi, vt_lo, ldvt, tau, t_hi, t_lo, tt_hi, tt_lo, ldt,
                  reinterpret_cast<unsigned long long*>(exchange), epoch, status, steps_taken, 0};
   if (rows_per_cta == 128) launch_pairs<32>(args, r, stream);

@@ -16,8 +16,8 @@ from . import kernels as k
 from . import local
 
 
-def _world() -> int:
-    return dist.get_world_size() if dist.is_initialized() else 1
+def _world(group=None) -> int:
+    return dist.get_world_size(group) if dist.is_initialized() else 1
 
 
 def _distributed():
@@ -32,32 +32,36 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
         update = local.soap_step(
             gradient_shard, state, global_shape=global_shape, beta=preconditioner_beta, beta1=beta1, beta2=beta2,
             eps=eps, interval=basis_refresh_interval, implementation=basis_implementation, initializing=initializing,
+        ).view(gradient_shard.shape)
+    else:
+        update = _distributed().soap_step(
+            gradient_shard, state, global_shape=global_shape, shard_dim=shard_dim, block_size=block_size, grid=grid,
+            beta=preconditioner_beta, beta1=beta1, beta2=beta2, eps=eps, interval=basis_refresh_interval,
+            implementation=basis_implementation, initializing=initializing,
         )
-        return update.view(gradient_shard.shape)
-    return _distributed().soap_step(
-        gradient_shard, state, global_shape=global_shape, shard_dim=shard_dim, block_size=block_size, grid=grid,
-        beta=preconditioner_beta, beta1=beta1, beta2=beta2, eps=eps, interval=basis_refresh_interval,
-        implementation=basis_implementation, initializing=initializing,
-    )
+    # Every bounded wait of the kernels reports through the device status word; look at the copy taken at the
+    # end of the previous step (no synchronisation) and raise SoapKernelError / SoapCommTimeout if it was set.
+    k.poll_status(gradient_shard.device)
+    return update
 
 
 def redistribute_tp_to_bc(matrix, global_shape, block_size, grid, shard_dim, group) -> Tensor:
-    if _world() == 1:
+    if _world(group) == 1:
         rows, cols = global_shape
         packed = empty_2d_block_cyclic_like_shape(rows, cols, dtype=torch.float32, device=matrix.device, zero=False)
         source = matrix if matrix.dtype == torch.float32 else matrix.float()
         k.gather2d(source, packed[:rows, :cols], None, None)
         return packed if matrix.dtype == torch.float32 else packed.to(matrix.dtype)
-    return _distributed().redistribute_tp_to_bc(matrix, global_shape, block_size, grid, shard_dim)
+    return _distributed().redistribute_tp_to_bc(matrix, global_shape, block_size, grid, shard_dim, group)
 
 
 def redistribute_bc_to_tp(matrix, global_shape, block_size, grid, shard_dim, group) -> Tensor:
-    if _world() == 1:
+    if _world(group) == 1:
         rows, cols = global_shape
         shard = torch.empty((rows, cols), dtype=torch.float32, device=matrix.device)
         k.gather2d(matrix[:rows, :cols].float(), shard, None, None)
         return shard.to(matrix.dtype)
-    return _distributed().redistribute_bc_to_tp(matrix, global_shape, block_size, grid, shard_dim)
+    return _distributed().redistribute_bc_to_tp(matrix, global_shape, block_size, grid, shard_dim, group)
 
 
 def rotate(matrix, Q_left, Q_right, global_shape, block_size, grid, direction) -> Tensor:
@@ -113,6 +117,6 @@ def initialize_basis(P, Q, work, eigenvalues, size, block_size, grid, implementa
 
 
 def permute(matrix, global_shape, row_order, column_order, block_size, grid, group) -> Tensor:
-    if _world() == 1:
+    if _world(group) == 1:
         return local.permute(matrix, global_shape, row_order, column_order)
-    return _distributed().permute(matrix, global_shape, row_order, column_order, block_size, grid)
+    return _distributed().permute(matrix, global_shape, row_order, column_order, block_size, grid, group)

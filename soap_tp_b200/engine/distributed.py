@@ -26,7 +26,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from ..layout import grid_coords, numroc, owned_indices
-from ..parallel.comm import Communicator, SymmetricSegment, get_communicator
+from ..parallel.comm import Communicator, SymmetricSegment, get_communicator, group_key
 from ..profiling import GLOBAL_STAGE_TIMER as TIMER
 from . import factor
 from . import kernels as k
@@ -100,8 +100,8 @@ def _packed_view(segment: SymmetricSegment, local_rows: int, local_cols: int) ->
 class GridEngine:
     """Distributed kernels' driver for one ``(device, grid, block_size)``."""
 
-    def __init__(self, device: torch.device, grid: Tuple[int, int], block_size: int) -> None:
-        self.comm: Communicator = get_communicator(device)
+    def __init__(self, device: torch.device, grid: Tuple[int, int], block_size: int, group=None) -> None:
+        self.comm: Communicator = get_communicator(device, group)
         self.device = torch.device(device)
         self.grid = grid
         self.nb = block_size
@@ -293,11 +293,14 @@ class GridEngine:
 _ENGINES: Dict[tuple, GridEngine] = {}
 
 
-def engine_for(device: torch.device, grid, block_size: int) -> GridEngine:
-    key = (str(torch.device(device)), tuple(grid), int(block_size))
+def engine_for(device: torch.device, grid, block_size: int, group=None) -> GridEngine:
+    """The engine of a grid over ``group`` (default: the world).  The ops that take ``group=`` (the two
+    redistributions and the permutation, as in the reference's ``src/soap_tp/ops/optimizer.py:71,229,404``)
+    pass it on; ranks, peers and barriers are then those of the group."""
+    key = (str(torch.device(device)), tuple(grid), int(block_size), group_key(group))
     engine = _ENGINES.get(key)
     if engine is None:
-        engine = GridEngine(device, tuple(grid), int(block_size))
+        engine = GridEngine(device, tuple(grid), int(block_size), group)
         _ENGINES[key] = engine
     return engine
 
@@ -309,8 +312,8 @@ def reset_engines() -> None:
 # ---------------------------------------------------------------------------------------------
 # Public-op entry points (each is collective and self-contained)
 # ---------------------------------------------------------------------------------------------
-def redistribute_tp_to_bc(matrix: Tensor, global_shape, block_size: int, grid, shard_dim: int) -> Tensor:
-    e = engine_for(matrix.device, grid, block_size)
+def redistribute_tp_to_bc(matrix: Tensor, global_shape, block_size: int, grid, shard_dim: int, group=None) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size, group)
     rows, cols = global_shape
     source = e.stage_shard(matrix, global_shape, shard_dim)
     e.comm.barrier()
@@ -334,8 +337,8 @@ def _pull_shard(e: GridEngine, source: Source, global_shape, shard_dim: int) -> 
     return shard
 
 
-def redistribute_bc_to_tp(matrix: Tensor, global_shape, block_size: int, grid, shard_dim: int) -> Tensor:
-    e = engine_for(matrix.device, grid, block_size)
+def redistribute_bc_to_tp(matrix: Tensor, global_shape, block_size: int, grid, shard_dim: int, group=None) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size, group)
     source = e.stage_packed("stage", matrix if matrix.dtype == torch.float32 else matrix.float(), global_shape)
     e.comm.barrier()
     shard = _pull_shard(e, source, global_shape, shard_dim)
@@ -359,10 +362,7 @@ def rotate(matrix: Tensor, Q_left: Tensor, Q_right: Tensor, global_shape, block_
 
 def gram_update(G_local: Tensor, preconditioner: Tensor, beta: float, block_size: int, grid, shard_dim: int, side: str) -> Tensor:
     e = engine_for(G_local.device, grid, block_size)
-    shape = torch.tensor(list(G_local.shape), dtype=torch.int64)
-    shapes = [torch.empty_like(shape) for _ in range(e.world)]
-    dist.all_gather(shapes, shape, group=e.comm.control)
-    dims = [tuple(int(v) for v in s.tolist()) for s in shapes]
+    dims = [tuple(d) for d in e.comm.gather_ints(list(G_local.shape))]
     replicated = 1 - shard_dim
     if any(d[replicated] != dims[0][replicated] for d in dims):
         raise ValueError(f"non-sharded dimension {replicated} must match on every rank.")
@@ -393,10 +393,8 @@ def gram_rows_from_col_shards(G_local: Tensor, out: Tensor, beta: float, side: s
     """
     world = dist.get_world_size()
     e = engine_for(G_local.device, (1, world), 128)
-    shape = torch.tensor(list(G_local.shape), dtype=torch.int64)
-    shapes = [torch.empty_like(shape) for _ in range(world)]
-    dist.all_gather(shapes, shape, group=e.comm.control)
-    if any(s.tolist() != shapes[0].tolist() for s in shapes):
+    shapes = e.comm.gather_ints(list(G_local.shape))
+    if any(s != shapes[0] for s in shapes):
         raise RuntimeError("every rank must hold a column shard of the same shape.")
     m, n_local = G_local.shape
     n = n_local * world
@@ -562,7 +560,7 @@ def _leader_of(job: int, jobs: int, world: int) -> int:
     return (job * world) // jobs
 
 
-def _factor_on_leaders(e: GridEngine, jobs, run) -> None:
+def _factor_on_leaders(e: GridEngine, jobs, run, long_running: bool = False) -> None:
     """Run independent dense factorisations concurrently, one per leader rank.
 
     ``jobs`` is a list of ``(packed input, packed output, size, column_order)``.  Every rank stages
@@ -586,7 +584,9 @@ def _factor_on_leaders(e: GridEngine, jobs, run) -> None:
             dense_in = _gather_dense(e, sources[index], size, order)
             dense_out = segment.local[: size * size].view(size, size).T
             run(index, dense_in, dense_out)
-    e.comm.barrier()
+    # the other ranks wait here for the leaders' factorisations: on the host when those can outlast the
+    # device barrier's spin budget (`long_running`: the eigensolver at initialisation)
+    e.comm.barrier(after_long_work=long_running)
     for (matrix, output, size, order), (segment, leader) in zip(jobs, results):
         table = e.leader_table(segment, leader)
         source = Source(segment, KIND_BLOCK_CYCLIC, size, size, 1, 1, 1, 1, 1)
@@ -646,7 +646,7 @@ def initialize_bases(e: GridEngine, jobs) -> None:
         factor.symmetric_eigenbasis(dense_in, dense_out, work, values, implementation)
         scratch[index] = values
 
-    _factor_on_leaders(e, [(P, Q, size, None) for P, Q, size, _, _ in jobs], run)
+    _factor_on_leaders(e, [(P, Q, size, None) for P, Q, size, _, _ in jobs], run, long_running=True)
     # eigenvalues live on the leader; hand them to everybody through a small segment
     for index, (_, _, size, values, _) in enumerate(jobs):
         leader = _leader_of(index, len(jobs), e.world)
@@ -667,8 +667,8 @@ def initialize_basis(P: Tensor, Q: Tensor, work: Tensor, eigenvalues: Tensor, si
     return Q
 
 
-def permute(matrix: Tensor, global_shape, row_order: Tensor, column_order: Tensor, block_size: int, grid) -> Tensor:
-    e = engine_for(matrix.device, grid, block_size)
+def permute(matrix: Tensor, global_shape, row_order: Tensor, column_order: Tensor, block_size: int, grid, group=None) -> Tensor:
+    e = engine_for(matrix.device, grid, block_size, group)
     rows, cols = global_shape
     source = e.stage_packed("stage", matrix, global_shape)
     e.comm.barrier()

@@ -31,6 +31,8 @@ STATUS_MESSAGES = {
     3: "GEMM epilogue timed out waiting for the accumulator",
     4: "cross-rank barrier timed out",
     5: "bad kernel argument",
+    6: "QR panel exchange between thread blocks timed out",
+    7: "wait for a peer's data-ready flag timed out",
 }
 
 LAUNCH_COUNTS: Dict[str, int] = {}
@@ -49,6 +51,10 @@ class SoapKernelError(RuntimeError):
     """A kernel of this library reported a bounded-wait timeout or a bad argument."""
 
 
+class SoapCommTimeout(SoapKernelError):
+    """A bounded device-side wait on a peer (barrier flag, data-ready flag) ran out."""
+
+
 _STATUS: Dict[int, Tensor] = {}
 
 
@@ -61,6 +67,11 @@ def status_word(device: torch.device) -> Tensor:
     return word
 
 
+def _raise_for(index: int, code: int) -> None:
+    kind = SoapCommTimeout if code in (4, 7) else SoapKernelError
+    raise kind(f"cuda:{index}: {STATUS_MESSAGES.get(code, f'status {code}')}")
+
+
 def check_status(device: Optional[torch.device] = None) -> None:
     """Synchronise and raise :class:`SoapKernelError` if any kernel gave up on a wait."""
     words = _STATUS.items() if device is None else [(device.index or 0, status_word(device))]
@@ -68,7 +79,54 @@ def check_status(device: Optional[torch.device] = None) -> None:
         code = int(word[0].item())
         if code != 0:
             word.zero_()
-            raise SoapKernelError(f"cuda:{index}: {STATUS_MESSAGES.get(code, f'status {code}')}")
+            _MONITORS.pop(index, None)
+            _raise_for(index, code)
+
+
+class _StatusMonitor:
+    """Deferred read-back of one device's status word: a 4-byte copy into pinned memory per step, looked at
+    one step later, so that a timed-out wait surfaces as an exception without a device synchronisation."""
+
+    def __init__(self, index: int, on_device: bool = True) -> None:
+        self.index = index
+        self.host = torch.zeros(2, dtype=torch.int32)
+        # `on_device=False` serves the host-side tests, which hand in a CPU tensor as the status word
+        self.events = [torch.cuda.Event(), torch.cuda.Event()] if on_device else None
+        if on_device:
+            self.host = self.host.pin_memory()
+        self.pending = [False, False]
+        self.turn = 0
+
+    def poll(self, word: Tensor) -> None:
+        previous = 1 - self.turn
+        if self.pending[previous]:
+            if self.events is not None:
+                self.events[previous].synchronize()   # recorded a whole step ago: already complete
+            self.pending[previous] = False
+            code = int(self.host[previous])
+            if code != 0:
+                word.zero_()
+                self.pending = [False, False]
+                _raise_for(self.index, code)
+        self.host[self.turn:self.turn + 1].copy_(word[:1], non_blocking=True)
+        if self.events is not None:
+            self.events[self.turn].record()
+        self.pending[self.turn] = True
+        self.turn = previous
+
+
+_MONITORS: Dict[int, _StatusMonitor] = {}
+
+
+def poll_status(device: torch.device) -> None:
+    """Called once per optimizer step on the step's stream.  Raises :class:`SoapKernelError` if the status
+    word copied at the end of the PREVIOUS step was non-zero, then enqueues this step's copy.  A failure is
+    therefore reported at most one step late and costs no synchronisation when nothing failed."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    monitor = _MONITORS.get(index)
+    if monitor is None:
+        monitor = _MONITORS[index] = _StatusMonitor(index)
+    monitor.poll(status_word(torch.device("cuda", index)))
 
 
 def mark_written(*tensors: Optional[Tensor]) -> None:

@@ -53,7 +53,9 @@ def _workspace(n: int, device, slot: int = 0) -> dict:
             "S": torch.zeros(PANEL * PANEL, dtype=torch.float32, device=device),
             "exchange": torch.zeros(8 * 160 * PANEL + 8 * PANEL, dtype=torch.float32, device=device),
             "partials": torch.empty(16 * PANEL * n, dtype=torch.float32, device=device),
-            "partials_q": None, "Zq": None, "Wq": None,    # forward accumulation of Q (allocated on first use)
+            # scratch of the forward accumulation of Q, which runs on a stream of its own
+            "partials_q": torch.empty(16 * PANEL * n, dtype=torch.float32, device=device),
+            "Zq": k.Planes.empty(PANEL, n, device), "Wq": k.Planes.empty(PANEL, n, device),
             "staging": torch.empty((n, n), dtype=torch.float32, device=device).T,
         }
         _WORKSPACES[key] = ws
@@ -219,9 +221,6 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
     if forward_q:
         # Q^T lives in the planes `Qp`; every panel's reflector is applied to its rows j0.. from the left,
         # exactly like the trailing matrix, on a stream of its own with its own scratch.
-        if ws["Zq"] is None:
-            ws["Zq"], ws["Wq"] = k.Planes.empty(PANEL, n, device), k.Planes.empty(PANEL, n, device)
-            ws["partials_q"] = torch.empty(16 * PANEL * n, dtype=torch.float32, device=device)
         q_stream = _q_stream(device, slot)
         q_stream.wait_event(start)
         with torch.cuda.stream(q_stream):

@@ -29,6 +29,7 @@ from torch import Tensor
 from . import _hostpath as host
 from .permute import permute_2d_block_cyclic_
 from .rotate import rotate_2d_block_cyclic_, validate_float_buffer, validate_world
+from ..parallel.guard import check_collective
 
 BASIS_IMPLEMENTATIONS = ("elpa", "eigh", "jacobi", "householder")
 
@@ -66,6 +67,7 @@ def estimated_eigenvalue_order_2d_block_cyclic_(
 
     The returned int64 tensor is identical on every rank; ties are broken by index (stable).
     """
+    check_collective("estimated_eigenvalue_order_2d_block_cyclic_", size, block_size, tuple(process_grid_shape))
     rank, _ = validate_world(process_grid_shape)
     buffers = (("preconditioner", preconditioner), ("Q", Q), ("work", work))
     for name, matrix in buffers:
@@ -104,6 +106,7 @@ def qr_2d_block_cyclic_(
     ``matrix`` is scratch afterwards.  Column signs are those of an unnormalised Householder
     factorisation (``R`` may have negative diagonal entries).
     """
+    check_collective("qr_2d_block_cyclic_", size, block_size, tuple(process_grid_shape))
     rank, _ = validate_world(process_grid_shape)
     for name, buffer in (("matrix", matrix), ("Q", Q)):
         validate_float_buffer(name, buffer, (size, size), block_size, process_grid_shape, rank)
@@ -134,6 +137,7 @@ def power_iteration_qr_2d_block_cyclic_(
     slate_binding: Optional[Any] = None,
 ) -> Tensor:
     """One power iteration: sort ``P Q`` by estimated eigenvalue, QR it into ``Q``; returns the order."""
+    check_collective("power_iteration_qr_2d_block_cyclic_", size, block_size, tuple(process_grid_shape))
     if preconditioner.is_cuda:
         # Validation happens inside the two public ops on the host path; the fused device path
         # validates once and folds the column permutation into the QR's panel gather.
@@ -174,6 +178,7 @@ def initialize_basis_2d_block_cyclic_(
     clobbered.  Unlike the reference's ELPA path there is no requirement that every rank owns
     at least one row and column, nor that the leading dimension is exact.
     """
+    check_collective("initialize_basis_2d_block_cyclic_", size, block_size, tuple(process_grid_shape), implementation)
     if implementation not in BASIS_IMPLEMENTATIONS:
         raise ValueError(
             f"implementation must be one of {BASIS_IMPLEMENTATIONS}, got {implementation!r}."
@@ -235,6 +240,7 @@ def refresh_bases_and_transport_optimizer_state_(
     in rotated coordinates) is permuted by the two eigenvalue orders.  Returns
     ``(left_order, right_order)``.
     """
+    check_collective("refresh_bases_and_transport_optimizer_state_", tuple(global_shape), block_size, tuple(process_grid_shape))
     rows, columns = global_shape
     grid = process_grid_shape
     rotate_2d_block_cyclic_(momentum, Q_left, Q_right, global_shape, block_size, grid, direction="backward")

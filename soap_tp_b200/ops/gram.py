@@ -23,6 +23,7 @@ from torch import Tensor
 
 from ..layout import validate_2d_block_cyclic_buffer
 from . import _hostpath as host
+from ..parallel.guard import check_collective
 
 
 def _check(G_local: Tensor, preconditioner: Tensor, beta: float, shard_dim: int, name: str) -> None:
@@ -69,6 +70,7 @@ def update_left_preconditioner_2d_block_cyclic_(
     shard_dim: Literal[0, 1],
 ) -> Tensor:
     """Update packed ``L = beta * L + (1 - beta) * G @ G.T`` in place."""
+    check_collective("update_left_preconditioner_2d_block_cyclic_", block_size, tuple(process_grid_shape), shard_dim, float(beta))
     return _update(G_local, left_preconditioner, beta, block_size, process_grid_shape, shard_dim, "left")
 
 
@@ -83,6 +85,7 @@ def update_right_preconditioner_2d_block_cyclic_(
     shard_dim: Literal[0, 1],
 ) -> Tensor:
     """Update packed ``R = beta * R + (1 - beta) * G.T @ G`` in place."""
+    check_collective("update_right_preconditioner_2d_block_cyclic_", block_size, tuple(process_grid_shape), shard_dim, float(beta))
     return _update(G_local, right_preconditioner, beta, block_size, process_grid_shape, shard_dim, "right")
 
 

@@ -21,6 +21,7 @@ from torch import Tensor
 
 from ..layout import local_2d_block_cyclic_shape
 from . import _hostpath as host
+from ..parallel.guard import check_collective
 
 
 def validated_permutation(order, size: int, name: str, device=None) -> Tensor:
@@ -58,6 +59,7 @@ def permute_2d_block_cyclic_(
     group=None,
 ) -> Tensor:
     """Apply ``matrix[row_order][:, column_order]`` to a packed matrix in place."""
+    check_collective("permute_2d_block_cyclic_", tuple(global_shape), block_size, tuple(process_grid_shape), group=group)
     if matrix.ndim != 2:
         raise ValueError(f"matrix must be 2D, got {matrix.ndim}D.")
     if block_size <= 0:

@@ -25,6 +25,7 @@ from ..layout import (
     local_2d_block_cyclic_shape,
 )
 from . import _hostpath as host
+from ..parallel.guard import check_collective
 
 
 def _common_checks(matrix: Tensor, global_shape, block_size, process_grid_shape, shard_dim, group):
@@ -63,6 +64,7 @@ def redistribute_tp_shard_to_2d_block_cyclic(
     group=None,
 ) -> Tensor:
     """Return the calling rank's packed block-cyclic part of a TP-sharded matrix."""
+    check_collective("redistribute_tp_shard_to_2d_block_cyclic", tuple(global_shape), block_size, tuple(process_grid_shape), shard_dim, group=group)
     rank, world_size = _common_checks(matrix, global_shape, block_size, process_grid_shape, shard_dim, group)
     rows, columns = global_shape
     expected = [rows, columns]
@@ -93,6 +95,7 @@ def redistribute_2d_block_cyclic_to_tp_shard(
     group=None,
 ) -> Tensor:
     """Return the calling rank's contiguous TP shard of a packed block-cyclic matrix."""
+    check_collective("redistribute_2d_block_cyclic_to_tp_shard", tuple(global_shape), block_size, tuple(process_grid_shape), shard_dim, group=group)
     rank, world_size = _common_checks(matrix, global_shape, block_size, process_grid_shape, shard_dim, group)
     local_rows, local_columns = local_2d_block_cyclic_shape(global_shape, block_size, process_grid_shape, rank)
     if matrix.size(0) < local_rows or matrix.size(1) < local_columns:

@@ -21,6 +21,7 @@ from torch import Tensor
 
 from ..layout import validate_2d_block_cyclic_buffer, validate_process_grid
 from . import _hostpath as host
+from ..parallel.guard import check_collective
 
 
 def validate_world(process_grid_shape: Tuple[int, int]) -> Tuple[int, int]:
@@ -53,6 +54,7 @@ def rotate_2d_block_cyclic_(
     ``slate_binding`` is accepted for call-site compatibility with the reference and ignored:
     there is no external GEMM library behind this op.
     """
+    check_collective("rotate_2d_block_cyclic_", tuple(global_shape), block_size, tuple(process_grid_shape), direction)
     if direction not in {"forward", "backward"}:
         raise ValueError(f"direction must be 'forward' or 'backward', got {direction!r}.")
     rank, _ = validate_world(process_grid_shape)

@@ -190,6 +190,22 @@ class SoapTP(torch.optim.Optimizer):
                 restored[name] = buffer
             restored["step"] = int(entry["step"])
             self.state[p] = restored
+        self._drop_device_caches()
+
+    @staticmethod
+    def _drop_device_caches() -> None:
+        """Operand planes of the bases are cached per buffer address and tensor version.  Freshly restored
+        buffers can reuse the addresses (and version numbers) of the ones they replace, so the caches are
+        emptied whenever state is loaded."""
+        import sys
+
+        local = sys.modules.get("soap_tp_b200.engine.local")
+        if local is not None:
+            local._CONTEXTS.clear()
+        distributed = sys.modules.get("soap_tp_b200.engine.distributed")
+        if distributed is not None:
+            for engine in distributed._ENGINES.values():
+                engine._basis_cache.clear()
 
 
 __all__ = ["SoapTP"]

@@ -27,8 +27,7 @@ from torch import Tensor
 from ..layout import Grid, validate_process_grid
 
 
-class SoapCommTimeout(RuntimeError):
-    """A bounded device-side wait on a peer ran out."""
+from ..engine.kernels import SoapCommTimeout  # noqa: E402  (re-exported: a bounded device-side wait on a peer ran out)
 
 
 class _RawBuffer:
@@ -50,18 +49,43 @@ class SymmetricSegment:
     peer_table: Tensor       # int64 device tensor of the same addresses (kernel argument)
 
 
+def default_barrier_timeout() -> float:
+    """Budget of one device-side barrier spin in seconds (``SOAP_TP_BARRIER_TIMEOUT_S``, default 30).
+
+    The spin only has to cover the skew between ranks that are all running device work; waits that can be
+    long by design (a leader rank factoring a whole matrix, a rank that saves a checkpoint) are taken on the
+    host first, see :meth:`Communicator.barrier`.  When the budget runs out the kernel sets the status word and
+    the next ``soap_step`` raises :class:`SoapCommTimeout`.
+    """
+    return float(os.environ.get("SOAP_TP_BARRIER_TIMEOUT_S", "30"))
+
+
 class Communicator:
-    def __init__(self, device: torch.device, *, barrier_timeout_s: float = 5.0) -> None:
+    def __init__(self, device: torch.device, *, group=None, barrier_timeout_s: Optional[float] = None) -> None:
+        """``group``: the process group whose ranks form the grid (default: the world).  Every rank of the group
+        must construct its communicator at the same point of the program."""
         from ..engine import kernels
 
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialized first.")
         self._C = kernels._C
         self.device = torch.device(device)
-        self.rank = dist.get_rank()
-        self.world = dist.get_world_size()
-        self.barrier_timeout_s = barrier_timeout_s
-        self.control = dist.group.WORLD if dist.get_backend() == "gloo" else dist.new_group(backend="gloo")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.barrier_timeout_s = default_barrier_timeout() if barrier_timeout_s is None else float(barrier_timeout_s)
+        # Control plane for small host-side exchanges.  A gloo-capable group serves as it is; for an NCCL-only
+        # world a gloo twin is created (collective over the world, which is where a world communicator is built);
+        # an NCCL-only sub-group is used directly -- object collectives and barriers work there through the device.
+        backend = str(dist.get_backend(group))
+        whole_world = group is None or group is dist.group.WORLD
+        if "gloo" in backend:
+            self.control = dist.group.WORLD if whole_world else group
+        elif whole_world:
+            self.control = dist.new_group(backend="gloo")
+        else:
+            self.control = group
+        self.control_on_device = "gloo" not in str(dist.get_backend(self.control))
         self.segments: Dict[str, SymmetricSegment] = {}
         self._epoch = 0
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
@@ -103,12 +127,21 @@ class Communicator:
         return seg
 
     # ---- ordering ----------------------------------------------------------------------------
-    def barrier(self) -> None:
+    def barrier(self, *, after_long_work: bool = False) -> None:
         """All work enqueued so far on every rank's current stream happens-before anything
-        enqueued after this call on any rank."""
+        enqueued after this call on any rank.
+
+        ``after_long_work``: some rank has just enqueued work that may take longer than the device barrier's
+        spin budget (a dense factorisation on a leader rank).  Every rank then first drains its own stream and
+        meets the others on the control plane, so the device-side spin that follows only covers microseconds
+        and cannot run out while a peer is still computing.
+        """
         if self.world == 1:
             return
         self.barrier_count += 1
+        if self.use_device_barrier and after_long_work:
+            torch.cuda.current_stream().synchronize()
+            dist.barrier(group=self.control)
         if self.use_device_barrier:
             from ..engine import kernels
 
@@ -125,29 +158,39 @@ class Communicator:
         """Synchronise and raise if a device-side wait timed out on this rank."""
         from ..engine import kernels
 
-        try:
-            kernels.check_status(self.device)
-        except kernels.SoapKernelError as error:
-            raise SoapCommTimeout(str(error)) from error
+        kernels.check_status(self.device)
+
+    def gather_ints(self, values: List[int]) -> List[List[int]]:
+        """The integer lists of every rank, in rank order (control plane)."""
+        everyone: List[Optional[List[int]]] = [None] * self.world
+        dist.all_gather_object(everyone, [int(v) for v in values], group=self.control)
+        return [list(v) for v in everyone]
 
     def all_equal(self, values: Tensor) -> bool:
-        """True if the int64 CPU tensor is identical on every rank (control plane)."""
+        """True if the int64 tensor is identical on every rank (control plane)."""
         if self.world == 1:
             return True
+        if self.control_on_device:
+            values = values.to(self.device)
         low, high = values.clone(), values.clone()
         dist.all_reduce(low, op=dist.ReduceOp.MIN, group=self.control)
         dist.all_reduce(high, op=dist.ReduceOp.MAX, group=self.control)
         return bool(torch.equal(low, high))
 
 
-_COMMUNICATORS: Dict[str, Communicator] = {}
+_COMMUNICATORS: Dict[tuple, Communicator] = {}
 
 
-def get_communicator(device: torch.device) -> Communicator:
-    key = str(torch.device(device))
+def group_key(group) -> int:
+    """Identity of a process group for caches (0: the world)."""
+    return 0 if group is None or group is dist.group.WORLD else id(group)
+
+
+def get_communicator(device: torch.device, group=None) -> Communicator:
+    key = (str(torch.device(device)), group_key(group))
     comm = _COMMUNICATORS.get(key)
     if comm is None:
-        comm = Communicator(torch.device(device))
+        comm = Communicator(torch.device(device), group=group)
         _COMMUNICATORS[key] = comm
     return comm
 

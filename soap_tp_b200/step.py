@@ -38,6 +38,7 @@ from .ops import (
     update_right_preconditioner_2d_block_cyclic_,
 )
 from .ops.basis import BASIS_IMPLEMENTATIONS
+from .parallel.guard import check_collective
 from .profiling import GLOBAL_STAGE_TIMER, profile_block_cyclic, profile_enabled, profile_tp_shard
 
 STATE_BUFFER_NAMES = (
@@ -106,6 +107,8 @@ def soap_step(
     rows, columns = global_shape
     grid = process_grid_shape
     initializing = "left_basis" not in state
+    check_collective("soap_step", tuple(global_shape), shard_dim, block_size, tuple(grid), basis_refresh_interval,
+                     basis_implementation, initializing, -1 if initializing else int(state["step"]))
     device = gradient_shard.device
     timer = GLOBAL_STAGE_TIMER
 

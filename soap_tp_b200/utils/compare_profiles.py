@@ -11,6 +11,14 @@ Input lines look like ``SOAP_PROFILE {"impl": "reference"|"tp", "step": k, "stag
 reference project use the same protocol (``src/soap_tp/soap.py:39-57``,
 ``tests/reference/soap.py:14-45``) and can be mixed in.
 
+Stage names are canonicalised first: the short names used by earlier instrumentation of the reference
+(``input.gradient``, ``adam.m``, ``soap_update``, ``left_basis_next`` ...; the reference's table is
+``scripts/compare_soap_profiles.py:35-79``) map onto the names this package writes.  A log that holds several
+comparisons one after the other (a parametrised test run: every shape writes its own trace with steps
+starting again at 0) is split into runs, each compared by itself (``scripts/compare_soap_profiles.py:227-253``):
+a new run starts at a ``gradient`` record whose (implementation, step) was already seen once both
+implementations have written something.
+
 Eigenvectors are defined up to sign.  For every step the tool derives one sign per basis column
 from the two ``left_basis`` / ``right_basis`` tensors and applies it to every tensor that lives in
 rotated coordinates (projected gradient, momentum, coordinate update) before comparing, as the
@@ -37,8 +45,28 @@ STAGES = [
     "momentum_before_adam", "variance_before_adam", "gradient_2d", "projected_gradient",
     "momentum_after_adam", "variance_after_adam", "coordinate_update", "backrotated_update", "returned_update",
     "left_preconditioner_after_step", "right_preconditioner_after_step", "left_basis_after_step",
-    "right_basis_after_step", "momentum_after_step", "variance_after_step",
+    "right_basis_after_step", "momentum_after_step", "variance_after_step", "parameter_after_step",
 ]
+# other spellings of the same taps -> the names above
+STAGE_ALIASES = {
+    "input.gradient": "gradient", "grad": "gradient",
+    "preconditioner.ema.0": "left_preconditioner", "preconditioner.ema.1": "right_preconditioner",
+    "basis.initial.output.0": "left_basis", "basis.initial.output.1": "right_basis",
+    "adam.m": "momentum_after_adam", "momentum": "momentum_after_adam",
+    "adam.v": "variance_after_adam", "variance": "variance_after_adam",
+    "projected_update": "coordinate_update", "soap_update": "returned_update", "update": "returned_update",
+    "left_preconditioner_next": "left_preconditioner_after_step",
+    "right_preconditioner_next": "right_preconditioner_after_step",
+    "left_basis_next": "left_basis_after_step", "right_basis_next": "right_basis_after_step",
+    "momentum_next": "momentum_after_step", "variance_next": "variance_after_step",
+    "parameter.after": "parameter_after_step",
+}
+
+
+def canonical_stage(name: str) -> str:
+    return STAGE_ALIASES.get(name, name)
+
+
 # stage -> which basis pair its coordinates refer to ("now": bases used by the step, "next": refreshed bases)
 ROTATED = {"projected_gradient": "now", "momentum_before_adam": "now", "momentum_after_adam": "now",
            "coordinate_update": "now", "momentum_after_step": "next"}
@@ -46,8 +74,9 @@ BASES = {"left_basis": ("now", 0), "right_basis": ("now", 1), "left_basis_after_
          "right_basis_after_step": ("next", 1)}
 
 
-def parse(paths: Iterable[str]) -> Dict[str, Dict[int, "OrderedDict[str, torch.Tensor]"]]:
-    traces: Dict[str, Dict[int, OrderedDict]] = {"reference": defaultdict(OrderedDict), "tp": defaultdict(OrderedDict)}
+def read_events(paths: Iterable[str]) -> List[Tuple[str, int, str, torch.Tensor]]:
+    """Every ``SOAP_PROFILE`` record of the logs, in file order: ``(implementation, step, stage, tensor)``."""
+    events: List[Tuple[str, int, str, torch.Tensor]] = []
     for path in paths:
         stream = sys.stdin if path == "-" else open(path)
         with stream:
@@ -64,8 +93,45 @@ def parse(paths: Iterable[str]) -> Dict[str, Dict[int, "OrderedDict[str, torch.T
                     continue
                 payload = record.get("tensor", record)
                 tensor = torch.tensor(payload["values"], dtype=torch.float64).reshape(payload["shape"])
-                traces[impl][int(record["step"])][str(record["stage"])] = tensor
+                events.append((impl, int(record["step"]), canonical_stage(str(record["stage"])), tensor))
+    return events
+
+
+def split_runs(events) -> List[list]:
+    """Cut a log that holds several comparisons back to back into one event list per comparison."""
+    runs: List[list] = []
+    current: list = []
+    seen, writers = set(), set()
+    for event in events:
+        impl, step, stage, _ = event
+        if stage == "gradient" and (impl, step, stage) in seen and writers == {"reference", "tp"}:
+            runs.append(current)
+            current, seen, writers = [], set(), set()
+        current.append(event)
+        seen.add((impl, step, stage))
+        writers.add(impl)
+    if current:
+        runs.append(current)
+    return runs
+
+
+def traces_of(events) -> Dict[str, Dict[int, "OrderedDict[str, torch.Tensor]"]]:
+    traces: Dict[str, Dict[int, OrderedDict]] = {"reference": defaultdict(OrderedDict), "tp": defaultdict(OrderedDict)}
+    for impl, step, stage, tensor in events:
+        traces[impl][step][stage] = tensor
     return traces
+
+
+def parse(paths: Iterable[str]) -> Dict[str, Dict[int, "OrderedDict[str, torch.Tensor]"]]:
+    """All records of the logs as one comparison (logs with a single run)."""
+    return traces_of(read_events(paths))
+
+
+def describe_run(events) -> str:
+    for impl, step, stage, tensor in events:
+        if stage == "gradient":
+            return "gradient shape " + "x".join(str(d) for d in tensor.shape)
+    return f"{len(events)} records"
 
 
 def column_signs(candidate: torch.Tensor, target: torch.Tensor) -> Tuple[torch.Tensor, float]:
@@ -128,7 +194,14 @@ def main(argv: Optional[List[str]] = None) -> int:
     parser.add_argument("logs", nargs="+", help="one or two log files ('-' for stdin)")
     parser.add_argument("--rtol", type=float, default=1e-5)
     args = parser.parse_args(argv)
-    return compare(parse(args.logs), args.rtol)
+    runs = split_runs(read_events(args.logs))
+    if len(runs) <= 1:
+        return compare(traces_of(runs[0] if runs else []), args.rtol)
+    worst = 0
+    for index, events in enumerate(runs):
+        print(f"=== run {index + 1} of {len(runs)}: {describe_run(events)} ===")
+        worst = max(worst, compare(traces_of(events), args.rtol))
+    return worst
 
 
 if __name__ == "__main__":

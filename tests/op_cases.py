@@ -345,3 +345,33 @@ def case_gram_1d_subgroups(rank, world, device_kind, shape, beta):
     eR = ((1 - beta) * fd.T @ fd)[local_rank * cols_here:(local_rank + 1) * cols_here]
     assert L.shape == (rows_here, rows) and R.shape == (cols_here, cols)
     assert relative_l2(L.cpu().double(), eL) < 1e-5 and relative_l2(R.cpu().double(), eR) < 1e-5
+
+
+def case_redistribute_permute_subgroups(rank, world, device_kind, shape, nb):
+    """``group=`` of the redistributions and the permutation: two independent halves of the world, each a
+    ``1 x half`` grid over its own process group with its own matrix
+    (the reference plumbs ``group`` through exactly these ops, ``src/soap_tp/ops/optimizer.py:71,229,404``)."""
+    assert world % 2 == 0
+    half = world // 2
+    groups = [dist.new_group(list(range(g * half, (g + 1) * half))) for g in range(2)]
+    mine = rank // half
+    group, local_rank = groups[mine], rank % half
+    grid = (1, half)
+    device = dev(device_kind, rank)
+    rows, cols = shape
+    full = seeded(shape, 41 + mine)
+    for shard_dim in (0, 1):
+        shard = full.chunk(half, dim=shard_dim)[local_rank].contiguous().to(device)
+        packed = ops.redistribute_tp_shard_to_2d_block_cyclic(shard, shape, nb, grid, shard_dim=shard_dim, group=group)
+        expected = pack(full, nb, grid, local_rank, device)
+        lr, lc = layout.local_2d_block_cyclic_shape(shape, nb, grid, local_rank)
+        assert torch.equal(packed[:lr, :lc], expected[:lr, :lc])
+        back = ops.redistribute_2d_block_cyclic_to_tp_shard(packed, shape, nb, grid, shard_dim=shard_dim, group=group)
+        assert torch.equal(back, shard)
+    g = torch.Generator().manual_seed(50 + mine)
+    ro, co = torch.randperm(rows, generator=g), torch.randperm(cols, generator=g)
+    X = pack(full, nb, grid, local_rank, device)
+    ops.permute_2d_block_cyclic_(X, shape, ro.to(device), co.to(device), nb, grid, group=group)
+    lr, lc = layout.local_2d_block_cyclic_shape(shape, nb, grid, local_rank)
+    want = pack(full[ro][:, co], nb, grid, local_rank, device)
+    assert torch.equal(X[:lr, :lc], want[:lr, :lc])

@@ -60,6 +60,7 @@ def test_four_ranks_ops():
     specs += [("case_initialize_basis", ((8, 12), "right", 2, GRID4, "eigh")),
               ("case_initialize_basis", ((9, 13), "left", 2, GRID4, "jacobi"))]
     specs += [("case_refresh", (shape, 2, GRID4)) for shape in [(8, 12), (13, 9)]]
+    specs += [("case_redistribute_permute_subgroups", ((12, 8), 2)), ("case_redistribute_permute_subgroups", ((260, 384), 64))]
     run_distributed(cases.case_batch, 4, "cuda", specs)
 
 

@@ -34,6 +34,7 @@ def test_gram_updates():
 def test_rotations_and_permutation():
     specs = [("case_rotate", (shape, 2, GRID)) for shape in RECT]
     specs += [("case_permute", (shape, 2, GRID)) for shape in [(8, 8), (9, 13)]]
+    specs += [("case_redistribute_permute_subgroups", ((12, 8), 2))]
     run_distributed(cases.case_batch, 4, "cpu", specs)
 
 

@@ -73,3 +73,32 @@ def test_timing_protocol(capsys):
     emit_timing("step", step=3, seconds=0.5)
     line = capsys.readouterr().out.strip()
     assert line == 'SOAP_TIMING {"event": "step", "seconds": 0.5, "step": 3}'
+
+
+def test_profile_diff_aliases_and_run_splitting(tmp_path, capsys):
+    """Short stage names are canonicalised, and a log holding two comparisons back to back (steps start again
+    at 0 with another shape) is compared run by run."""
+    from soap_tp_b200.utils import compare_profiles
+
+    def record(impl, step, stage, tensor):
+        body = {"impl": impl, "step": step, "stage": stage, "shape": list(tensor.shape), "dtype": "float32",
+                "values": tensor.flatten().tolist()}
+        return "SOAP_PROFILE " + json.dumps(body, separators=(",", ":"))
+
+    lines = []
+    for shape in ((2, 3), (4, 2)):
+        g = torch.arange(float(shape[0] * shape[1])).reshape(shape)
+        for step in (0, 1):
+            lines += [record("ref", step, "input.gradient", g + step), record("reference", step, "soap_update", g * 2)]
+            lines += [record("src", step, "gradient", g + step), record("tp", step, "returned_update", g * 2)]
+    log = tmp_path / "two_runs.log"
+    log.write_text("\n".join(lines) + "\n")
+    events = compare_profiles.read_events([str(log)])
+    assert {stage for _, _, stage, _ in events} == {"gradient", "returned_update"}
+    runs = compare_profiles.split_runs(events)
+    assert [compare_profiles.describe_run(r) for r in runs] == ["gradient shape 2x3", "gradient shape 4x2"]
+    assert compare_profiles.main([str(log)]) == 0
+    out = capsys.readouterr().out
+    assert "=== run 1 of 2: gradient shape 2x3 ===" in out and "=== run 2 of 2: gradient shape 4x2 ===" in out
+    assert "SHAPE MISMATCH" not in out
+    assert compare_profiles.canonical_stage("adam.v") == "variance_after_adam"

@@ -1,0 +1,48 @@
+"""Host-side tests of the deferred status read-back (no GPU: the status word is a CPU tensor here).
+
+Every bounded wait of the kernels reports through one int32 status word per device; ``poll_status`` is
+what turns a non-zero word into an exception inside ``soap_step`` one step later.
+"""
+import pytest
+import torch
+
+from soap_tp_b200.engine import kernels
+
+
+def test_monitor_raises_one_poll_after_the_word_was_set():
+    word = torch.zeros(4, dtype=torch.int32)
+    monitor = kernels._StatusMonitor(0, on_device=False)
+    monitor.poll(word)          # step 1: clean
+    monitor.poll(word)          # step 2: clean
+    word[0] = 4                 # a barrier gave up during step 3
+    monitor.poll(word)          # end of step 3: the copy is taken, nothing is raised yet
+    with pytest.raises(kernels.SoapCommTimeout, match="barrier timed out"):
+        monitor.poll(word)      # end of step 4: the copy of step 3 is read
+    assert int(word[0]) == 0    # cleared, so that a caller who handles the error can go on
+    monitor.poll(word)
+    monitor.poll(word)
+
+
+@pytest.mark.parametrize("code,kind", [(1, kernels.SoapKernelError), (6, kernels.SoapKernelError),
+                                       (7, kernels.SoapCommTimeout)])
+def test_monitor_maps_codes_to_exception_types(code, kind):
+    word = torch.zeros(4, dtype=torch.int32)
+    monitor = kernels._StatusMonitor(0, on_device=False)
+    word[0] = code
+    monitor.poll(word)
+    with pytest.raises(kind) as caught:
+        monitor.poll(word)
+    assert kernels.STATUS_MESSAGES[code] in str(caught.value)
+    assert issubclass(kernels.SoapCommTimeout, kernels.SoapKernelError)
+
+
+def test_poll_status_uses_the_device_word(monkeypatch):
+    word = torch.zeros(4, dtype=torch.int32)
+    monkeypatch.setattr(kernels, "status_word", lambda device: word)
+    monkeypatch.setitem(kernels._MONITORS, 0, kernels._StatusMonitor(0, on_device=False))
+    device = torch.device("cuda", 0)
+    kernels.poll_status(device)
+    word[0] = 3
+    kernels.poll_status(device)
+    with pytest.raises(kernels.SoapKernelError, match="accumulator"):
+        kernels.poll_status(device)

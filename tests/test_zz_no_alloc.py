@@ -81,6 +81,25 @@ def test_no_alloc_entry_point_matches_regular_entry_point_twice():
     _factor_both(k, entry, 700, 96, seed=2)       # second call: fewer blocks, the scratch holds stale words
 
 
+def test_no_alloc_entry_point_at_its_documented_maximum():
+    """16384 rows x 128 columns: 64 thread blocks, every word of the built-in scratch is in use."""
+    k, entry = _load()
+    _factor_both(k, entry, 16384, 128, seed=3)
+    _factor_both(k, entry, 16384, 128, seed=4)    # again, over the previous call's words
+
+
+def test_no_alloc_entry_point_on_a_second_device():
+    """The scratch address is resolved per device, and the kernel's shared-memory limit is raised per device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    k, entry = _load()
+    with torch.cuda.device(1):
+        _factor_both_on = lambda: _factor_both(k, entry, 1500, 128, seed=5)
+        # tensors created with device="cuda" follow the current device
+        _factor_both_on()
+        _factor_both_on()
+
+
 def test_no_alloc_entry_point_refuses_oversized_panels():
     k, entry = _load()
     dummy = torch.zeros(8, device="cuda")
