@@ -341,6 +341,7 @@ def run(args: argparse.Namespace) -> int:
     fence()
     e2e_ms = torch.tensor([(time.perf_counter() - e2e_start) * 1e3], dtype=torch.float64, device=device)
     dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_step_ms = [round(t, 3) for t in max_over_ranks(loop_marks[i].elapsed_time(loop_marks[i + 1]) for i in range(steps_done))]
     if single_loop:
         device_ms = torch.tensor([loop_start.elapsed_time(loop_stop)], dtype=torch.float64, device=device)
         dist.all_reduce(device_ms, op=dist.ReduceOp.MAX)
@@ -432,6 +433,7 @@ def run(args: argparse.Namespace) -> int:
                 "unit": "ms/step",
                 "h2d_bytes_per_step": shard_bytes,
                 "d2h_bytes_per_step": 4,
+                "step_ms": e2e_step_ms,
             },
             "gpu_launches": int(launches_timed),
         }

@@ -7,6 +7,8 @@
     python -m soap_tp_b200.bench.kernel_cases update --size 4096      # QR trailing update (K = 128, planes RMW)
     python -m soap_tp_b200.bench.kernel_cases adam --size 8192
     python -m soap_tp_b200.bench.kernel_cases split --size 8192
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m soap_tp_b200.bench.kernel_cases \
+        gather --size 8192                                          # peer pull, traffic mix of an 8-GPU (2, 4) grid
 
 Each case allocates a few hundred MB at most, launches the kernel ``--repeats`` times and prints
 the CUDA-event time per launch, so the same command line serves for timing and, under ``ncu -k
@@ -32,9 +34,67 @@ def timed(fn, repeats: int) -> float:
     return start.elapsed_time(stop) / repeats * 1e3
 
 
+def gather_case(args) -> int:
+    """Time ``dist_gather_kernel`` on the three pulls of a steady step as rank 0 of an 8-rank (2, 4) grid sees
+    them: one eighth of the source is local, seven eighths sit in a peer GPU's memory.  Needs two ranks (two
+    GPUs); each holds the seven remote shards its partner reads.  Prints microseconds and GB/s of source bytes
+    for the 16-byte kernels and for the element-wise kernel."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..engine import kernels as k
+    from ..parallel.comm import get_communicator
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+    if dist.get_world_size() != 2:
+        raise SystemExit("the gather case needs exactly two ranks")
+    rank = dist.get_rank()
+    comm = get_communicator(device)
+    n, nb, virtual, Pr, Pc = args.size, 128, 8, 2, 4
+    shard = n * n // virtual
+    segment = comm.segment("gather_case", virtual * shard)
+    segment.local.normal_()
+    comm.barrier()
+    # virtual rank 0's data is mine, virtual ranks 1..7 live in the partner's segment
+    partner = segment.peer_ptrs[1 - rank]
+    table = torch.tensor([segment.peer_ptrs[rank]] + [partner + 4 * v * shard for v in range(1, virtual)],
+                         dtype=torch.int64, device=device)
+    planes = k.Planes.empty(n, n // Pr, device)
+    stream = lambda: torch.cuda.current_stream().cuda_stream
+
+    def pull(kind, cols_out, jP, transpose):
+        k._C.dist_gather(table.data_ptr(), kind, n, n, nb, nb, Pr, Pc, virtual, 0, 1, 1, 0, 0, 0, jP, nb, 0, 0,
+                         int(transpose), 0, 0, 0, planes.hi.data_ptr(), planes.lo.data_ptr(), 1, planes.ld, n, cols_out,
+                         stream())
+
+    cases = [("gradient panel from column shards (turn)", 2, n // Pr, Pr, False),
+             ("intermediate from packed blocks (copy)", 0, n // Pr, Pr, False),
+             ("Gram operand from column shards, transposed (copy)", 2, n // Pc, Pc, True)]
+    for name, kind, cols_out, jP, transpose in cases:
+        for scalar in (False, True):
+            k._C.force_scalar_gather(scalar)
+            us = timed(lambda: pull(kind, cols_out, jP, transpose), args.repeats)
+            best = torch.tensor([us], device=device)
+            dist.all_reduce(best, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                bytes_read = 4.0 * n * cols_out
+                print(f"{name}: {'element-wise' if scalar else '16-byte'} {float(best):.1f} us, "
+                      f"{bytes_read / float(best) / 1e3:.0f} GB/s of source bytes ({bytes_read * 7 / 8 / float(best) / 1e3:.0f} "
+                      f"GB/s over NVLink), {3 * bytes_read / float(best) / 1e6:.2f} TB/s of local traffic incl. both planes")
+        k._C.force_scalar_gather(False)
+    comm.barrier()
+    k.check_status()
+    dist.destroy_process_group()
+    return 0
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("case", choices=("gemm", "qr", "qrpair", "panel", "update", "adam", "split"))
+    parser.add_argument("case", choices=("gemm", "qr", "qrpair", "panel", "update", "adam", "split", "gather"))
     parser.add_argument("--size", type=int, default=4096)
     parser.add_argument("--rows", type=int, default=4096)
     parser.add_argument("--mode", default="store")
@@ -48,6 +108,8 @@ def main(argv=None) -> int:
     from ..engine import kernels as k
     from ..engine import qr
 
+    if args.case == "gather":
+        return gather_case(args)
     n = args.size
     device = torch.device("cuda", torch.cuda.current_device())
     generator = torch.Generator(device=device).manual_seed(0)

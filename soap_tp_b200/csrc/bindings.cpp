@@ -150,8 +150,11 @@ PYBIND11_MODULE(_C, m) {
           sum_partials_to_planes(ptr<const float>(partials), splits, stride, ld, ptr<float>(hi), ptr<float>(lo), ldp, rows,
                                  cols, stream_of(stream));
         });
-  m.def("identity_planes", [](uint64_t hi, uint64_t lo, int64_t ldp, int rows, int cols, uint64_t stream) {
-    identity_planes(ptr<float>(hi), ptr<float>(lo), ldp, rows, cols, stream_of(stream));
+  m.def("identity_planes", [](uint64_t hi, uint64_t lo, int64_t ldp, int rows, int cols, uint64_t stream, int first_col) {
+    identity_planes(ptr<float>(hi), ptr<float>(lo), ldp, rows, cols, stream_of(stream), first_col);
+  }, py::arg("hi"), py::arg("lo"), py::arg("ldp"), py::arg("rows"), py::arg("cols"), py::arg("stream"), py::arg("first_col") = 0);
+  m.def("planes_sum", [](uint64_t hi, uint64_t lo, int64_t ldp, uint64_t out, int64_t ldo, int depth, int cols, uint64_t stream) {
+    planes_sum(ptr<const float>(hi), ptr<const float>(lo), ldp, ptr<float>(out), ldo, depth, cols, stream_of(stream));
   });
   m.attr("QR_PANEL_WIDTH") = kQrPanelWidth;
   m.attr("QR_ROWS_PER_CTA") = kQrRowsPerCta;

@@ -28,6 +28,7 @@
 #include <cstring>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 #include "comm.h"
 #include "ptx.cuh"
@@ -36,6 +37,8 @@ namespace py = pybind11;
 
 namespace soapb200 {
 namespace {
+
+bool g_force_scalar_gather = false;   // tests: route every gather through the element-wise kernel
 
 void check(cudaError_t err, const char* what) {
   if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
@@ -76,7 +79,8 @@ __device__ __forceinline__ int numroc_dev(int n, int nb, int p, int P) {
   return count;
 }
 
-__device__ __forceinline__ float load_source(const DistSource& src, int gi, int gj) {
+// Address of element (gi, gj) of the distributed matrix in the owner's segment.
+__device__ __forceinline__ const float* source_address(const DistSource& src, int gi, int gj) {
   const float* base;
   int64_t offset;
   if (src.kind == kBlockCyclic) {
@@ -97,7 +101,11 @@ __device__ __forceinline__ float load_source(const DistSource& src, int gi, int 
     base = src.peers[gj / per];
     offset = static_cast<int64_t>(gi) * per + gj % per;
   }
-  return __ldcg(base + offset);  // bypass L1: peers rewrite these buffers between launches
+  return base + offset;
+}
+
+__device__ __forceinline__ float load_source(const DistSource& src, int gi, int gj) {
+  return __ldcg(source_address(src, gi, gj));  // bypass L1: peers rewrite these buffers between launches
 }
 
 __device__ __forceinline__ float tf32_round_dev(float x) {
@@ -142,6 +150,113 @@ dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose
   }
 }
 
+// ---- 16-byte paths ---------------------------------------------------------------------------------
+// Both kernels below need what the host checks in `vector_path_allowed`: no permutation vectors, no triangle
+// mask, output pitch 1 along i with 16-byte aligned columns, and index maps under which four consecutive
+// 4-aligned local indices along the source's contiguous axis stay four consecutive 4-aligned global indices
+// inside one block / one shard.  A group whose source address still is not 16-byte aligned (a peer whose local
+// pitch is odd) or that crosses the end of the output falls back to element loads inside the kernel.
+__device__ __forceinline__ float4 load_group(const DistSource& src, bool transpose, int a, int b, int limit) {
+  // four elements along the first mapped index a .. a+3 (only the first `limit` are needed)
+  const float* p = transpose ? source_address(src, b, a) : source_address(src, a, b);
+  if (limit >= 4 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) return __ldcg(reinterpret_cast<const float4*>(p));
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  v.x = __ldcg(p);
+  if (limit > 1) v.y = transpose ? load_source(src, b, a + 1) : load_source(src, a + 1, b);
+  if (limit > 2) v.z = transpose ? load_source(src, b, a + 2) : load_source(src, a + 2, b);
+  if (limit > 3) v.w = transpose ? load_source(src, b, a + 3) : load_source(src, a + 3, b);
+  return v;
+}
+
+__device__ __forceinline__ void store_group(float* out_hi, float* out_lo, int64_t off, const float4& x, int limit) {
+  if (limit >= 4) {
+    if (out_lo) {
+      const float4 h = make_float4(tf32_round_dev(x.x), tf32_round_dev(x.y), tf32_round_dev(x.z), tf32_round_dev(x.w));
+      *reinterpret_cast<float4*>(out_hi + off) = h;
+      *reinterpret_cast<float4*>(out_lo + off) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+    } else {
+      *reinterpret_cast<float4*>(out_hi + off) = x;
+    }
+    return;
+  }
+  const float v[4] = {x.x, x.y, x.z, x.w};
+  for (int e = 0; e < limit; ++e) {
+    if (out_lo) {
+      const float h = tf32_round_dev(v[e]);
+      out_hi[off + e] = h;
+      out_lo[off + e] = v[e] - h;
+    } else {
+      out_hi[off + e] = v[e];
+    }
+  }
+}
+
+// Source contiguous along i (as the output is): a warp moves 512 contiguous bytes of one output column per
+// pass, four passes (four columns) in flight per thread; no shared memory.
+constexpr int kCopyTileI = 128, kCopyTileJ = 32;
+__global__ void __launch_bounds__(256)
+dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, float* out_hi, float* out_lo,
+                          int64_t d_j, int rows_out, int cols_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int i = blockIdx.x * kCopyTileI + 4 * lane;
+  if (i >= rows_out) return;
+  const int limit = min(4, rows_out - i);
+  const int a = map_index(map_i, i);
+  const int j0 = blockIdx.y * kCopyTileJ + warp;
+  float4 v[4];
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int j = j0 + 8 * pass;
+    if (j < cols_out) v[pass] = load_group(src, transpose != 0, a, map_index(map_j, j), limit);
+  }
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int j = j0 + 8 * pass;
+    if (j < cols_out) store_group(out_hi, out_lo, i + static_cast<int64_t>(j) * d_j, v[pass], limit);
+  }
+}
+
+// Source contiguous along j: 64 x 64 tile, read as 256-byte rows along j, turned in shared memory, written
+// as 16-byte groups along i.
+constexpr int kTurnTile = 64;
+__global__ void __launch_bounds__(256)
+dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, float* out_hi, float* out_lo,
+                          int64_t d_j, int rows_out, int cols_out) {
+  __shared__ float tile[kTurnTile][kTurnTile + 1];   // [i][j]
+  const int i0 = blockIdx.x * kTurnTile, j0 = blockIdx.y * kTurnTile;
+  const int group = threadIdx.x & 15, line = threadIdx.x >> 4;
+  {
+    const int j = j0 + 4 * group;
+    const int limit = min(4, cols_out - j);
+    const int b = (limit > 0) ? map_index(map_j, j) : 0;
+    float4 v[4];
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      const int i = i0 + line + 16 * pass;
+      v[pass] = make_float4(0.f, 0.f, 0.f, 0.f);
+      // the group runs along the SECOND mapped index here: swap the roles for load_group
+      if (i < rows_out && limit > 0) v[pass] = load_group(src, transpose == 0, b, map_index(map_i, i), limit);
+    }
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      float* row = &tile[line + 16 * pass][4 * group];
+      row[0] = v[pass].x; row[1] = v[pass].y; row[2] = v[pass].z; row[3] = v[pass].w;
+    }
+  }
+  __syncthreads();
+  const int i = i0 + 4 * group;
+  const int limit = min(4, rows_out - i);
+  if (limit <= 0) return;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int jl = line + 16 * pass, j = j0 + jl;
+    if (j < cols_out) {
+      const float4 x = make_float4(tile[4 * group][jl], tile[4 * group + 1][jl], tile[4 * group + 2][jl], tile[4 * group + 3][jl]);
+      store_group(out_hi, out_lo, i + static_cast<int64_t>(j) * d_j, x, limit);
+    }
+  }
+}
+
 // ---- cross-rank barrier ----------------------------------------------------------------------
 __global__ void barrier_kernel(int* const* pads, int rank, int world, int epoch, int* status, long long budget_ns) {
   const int peer = threadIdx.x;
@@ -162,6 +277,33 @@ __global__ void barrier_kernel(int* const* pads, int rank, int world, int epoch,
       break;
     }
     __nanosleep(200);
+  }
+  __threadfence_system();
+}
+
+// ---- one-way flags: a producer rank announces progress, consumer ranks wait for it -----------------
+// The flag is an int32 in the PRODUCER's symmetric segment.  `signal_flag_kernel` runs on the producer's stream
+// after the work it announces; `wait_flag_kernel` runs on a consumer's stream and polls the producer's memory
+// over NVLink with a time budget.  Used only when every rank has its own GPU (a consumer that waited for a
+// producer kernel queued behind it on the same GPU would never see the flag).
+__global__ void signal_flag_kernel(int* flag, int value) {
+  __threadfence_system();
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+
+__global__ void wait_flag_kernel(const int* flag, int value, int* status, long long budget_ns) {
+  unsigned long long start, now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen - value >= 0) break;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (static_cast<long long>(now - start) > budget_ns) {
+      atomicCAS(status, 0, kStatusPeerFlagTimeout);
+      break;
+    }
+    __nanosleep(500);
   }
   __threadfence_system();
 }
@@ -202,17 +344,63 @@ void register_comm(py::module_& m) {
           DistSource src{reinterpret_cast<const float* const*>(peers), kind, rows, cols, nb_r, nb_c, Pr, Pc, world};
           IndexMap mi{ip, iP, inb, ioff, reinterpret_cast<const int64_t*>(iperm), i_local_offset};
           IndexMap mj{jp, jP, jnb, joff, reinterpret_cast<const int64_t*>(jperm), j_local_offset};
+          if (!upper_only && d_i != 1 && d_j == 1) {
+            // a row-major output is the column-major output of the transposed problem: out'(j, i) = out(i, j)
+            std::swap(mi, mj);
+            std::swap(rows_out, cols_out);
+            std::swap(d_i, d_j);
+            transpose = !transpose;
+          }
           // consecutive i are consecutive in the source when i indexes the source's contiguous dimension:
           // rows for column-major packed buffers, columns for row-major shards.
           const bool i_is_source_row = !transpose;
           const bool source_row_contiguous = (kind == kBlockCyclic);
           const int read_i_fast = (i_is_source_row == source_row_contiguous) ? 1 : 0;
+          cudaStream_t cuda_stream = reinterpret_cast<cudaStream_t>(stream);
+          // 16-byte paths: see the comment above load_group for what has to hold
+          auto keeps_groups = [](const IndexMap& m) {
+            return m.perm == nullptr && m.offset % 4 == 0 && m.local_offset % 4 == 0 && (m.P <= 1 || m.nb % 4 == 0);
+          };
+          const IndexMap& along = read_i_fast ? mi : mj;     // the map along the source's contiguous axis
+          bool source_groups;                                // a 4-aligned global group stays in one block / shard
+          if (kind == kBlockCyclic) source_groups = (nb_r % 4 == 0);
+          else if (kind == kRowShards) source_groups = (cols % 4 == 0);
+          else source_groups = (world > 0 && (cols / world) % 4 == 0);
+          const bool aligned_out = d_i == 1 && d_j % 4 == 0 && (out_hi % 16 == 0) && (out_lo % 16 == 0);
+          if (!upper_only && mi.perm == nullptr && mj.perm == nullptr && keeps_groups(along) && source_groups && aligned_out &&
+              !g_force_scalar_gather) {
+            if (read_i_fast) {
+              dim3 grid((rows_out + kCopyTileI - 1) / kCopyTileI, (cols_out + kCopyTileJ - 1) / kCopyTileJ);
+              dist_gather_copy16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, reinterpret_cast<float*>(out_hi),
+                                                                      reinterpret_cast<float*>(out_lo), d_j, rows_out, cols_out);
+              check(cudaGetLastError(), "dist_gather_copy16_kernel");
+            } else {
+              dim3 grid((rows_out + kTurnTile - 1) / kTurnTile, (cols_out + kTurnTile - 1) / kTurnTile);
+              dist_gather_turn16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, reinterpret_cast<float*>(out_hi),
+                                                                      reinterpret_cast<float*>(out_lo), d_j, rows_out, cols_out);
+              check(cudaGetLastError(), "dist_gather_turn16_kernel");
+            }
+            return;
+          }
           dim3 grid((rows_out + 31) / 32, (cols_out + 31) / 32);
           dist_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
               src, mi, mj, transpose, read_i_fast, upper_only, reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), d_i,
               d_j, rows_out, cols_out);
           check(cudaGetLastError(), "dist_gather_kernel");
         });
+
+  m.def("signal_flag", [](uint64_t flag, int value, uint64_t stream) {
+    signal_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int*>(flag), value);
+    check(cudaGetLastError(), "signal_flag_kernel");
+  });
+  m.def("wait_flag", [](uint64_t flag, int value, uint64_t status, double budget_seconds, uint64_t stream) {
+    wait_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const int*>(flag), value, reinterpret_cast<int*>(status), static_cast<long long>(budget_seconds * 1e9));
+    check(cudaGetLastError(), "wait_flag_kernel");
+  });
+
+  m.def("force_scalar_gather", [](bool on) { g_force_scalar_gather = on; },
+        "Route every dist_gather through the element-wise kernel (cross-checks of the 16-byte paths)");
 
   m.def("device_barrier", [](uint64_t pads, int rank, int world, int epoch, uint64_t status, double budget_seconds,
                              uint64_t stream) {

@@ -317,14 +317,27 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int spli
   }
 }
 
-__global__ void identity_planes_kernel(float* hi, float* lo, int64_t ldp, int rows, int cols) {
+__global__ void identity_planes_kernel(float* hi, float* lo, int64_t ldp, int rows, int cols, int first_col) {
   const int64_t total = static_cast<int64_t>(rows) * cols;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int i = static_cast<int>(idx % rows);
     const int64_t c = idx / rows;
-    hi[i + c * ldp] = (i == c) ? 1.f : 0.f;
+    hi[i + c * ldp] = (i == c + first_col) ? 1.f : 0.f;
     lo[i + c * ldp] = 0.f;
+  }
+}
+
+// out[c * ldo + k] = hi[k + c * ldp] + lo[k + c * ldp]: the fp32 matrix behind operand planes, each plane
+// column written as one contiguous output row (planes of Q^T read out as Q).
+__global__ void planes_sum_kernel(const float* __restrict__ hi, const float* __restrict__ lo, int64_t ldp, float* out,
+                                  int64_t ldo, int depth, int cols) {
+  const int64_t total = static_cast<int64_t>(depth) * cols;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int k = static_cast<int>(idx % depth);
+    const int64_t c = idx / depth;
+    out[c * ldo + k] = hi[k + c * ldp] + lo[k + c * ldp];
   }
 }
 
@@ -372,10 +385,17 @@ void sum_partials_to_planes(const float* partials, int splits, int64_t stride, i
   check_launch("sum_partials_kernel");
 }
 
-void identity_planes(float* hi, float* lo, int64_t ldp, int rows, int cols, cudaStream_t stream) {
+void identity_planes(float* hi, float* lo, int64_t ldp, int rows, int cols, cudaStream_t stream, int first_col) {
   if (rows <= 0 || cols <= 0) return;
-  identity_planes_kernel<<<grid_for(static_cast<int64_t>(rows) * cols), 256, 0, stream>>>(hi, lo, ldp, rows, cols);
+  identity_planes_kernel<<<grid_for(static_cast<int64_t>(rows) * cols), 256, 0, stream>>>(hi, lo, ldp, rows, cols, first_col);
   check_launch("identity_planes_kernel");
+}
+
+void planes_sum(const float* hi, const float* lo, int64_t ldp, float* out, int64_t ldo, int depth, int cols,
+                cudaStream_t stream) {
+  if (depth <= 0 || cols <= 0) return;
+  planes_sum_kernel<<<grid_for(static_cast<int64_t>(depth) * cols), 256, 0, stream>>>(hi, lo, ldp, out, ldo, depth, cols);
+  check_launch("planes_sum_kernel");
 }
 
 }  // namespace soapb200

@@ -37,7 +37,12 @@ void qr_panel_pairs(const float* p_hi, const float* p_lo, int64_t ldp, int r, in
 void sum_partials_to_planes(const float* partials, int splits, int64_t stride, int64_t ld, float* hi, float* lo,
                             int64_t ldp, int rows, int cols, cudaStream_t stream);
 
-// planes <- identity (rows x cols).
-void identity_planes(float* hi, float* lo, int64_t ldp, int rows, int cols, cudaStream_t stream);
+// planes <- columns first_col .. first_col + cols - 1 of the rows x rows identity.
+void identity_planes(float* hi, float* lo, int64_t ldp, int rows, int cols, cudaStream_t stream, int first_col = 0);
+
+// out[c * ldo + k] = hi[k + c * ldp] + lo[k + c * ldp] for k < depth, c < cols (the fp32 values behind operand
+// planes, every plane column as one contiguous row of `out`).
+void planes_sum(const float* hi, const float* lo, int64_t ldp, float* out, int64_t ldo, int depth, int cols,
+                cudaStream_t stream);
 
 }  // namespace soapb200
