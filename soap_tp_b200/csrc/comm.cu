@@ -151,8 +151,8 @@ dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose
 }
 
 // ---- 16-byte paths ---------------------------------------------------------------------------------
-// Both kernels below need what the host checks in `vector_path_allowed`: no permutation vectors, no triangle
-// mask, output pitch 1 along i with 16-byte aligned columns, and index maps under which four consecutive
+// Both kernels below need what the host checks before choosing them: no permutation vector along the source's
+// contiguous axis (one along the other axis is fine), no triangle mask, output pitch 1 along i with 16-byte aligned columns, and index maps under which four consecutive
 // 4-aligned local indices along the source's contiguous axis stay four consecutive 4-aligned global indices
 // inside one block / one shard.  A group whose source address still is not 16-byte aligned (a peer whose local
 // pitch is odd) or that crosses the end of the output falls back to element loads inside the kernel.
@@ -367,7 +367,7 @@ void register_comm(py::module_& m) {
           else if (kind == kRowShards) source_groups = (cols % 4 == 0);
           else source_groups = (world > 0 && (cols / world) % 4 == 0);
           const bool aligned_out = d_i == 1 && d_j % 4 == 0 && (out_hi % 16 == 0) && (out_lo % 16 == 0);
-          if (!upper_only && mi.perm == nullptr && mj.perm == nullptr && keeps_groups(along) && source_groups && aligned_out &&
+          if (!upper_only && keeps_groups(along) && source_groups && aligned_out &&
               !g_force_scalar_gather) {
             if (read_i_fast) {
               dim3 grid((rows_out + kCopyTileI - 1) / kCopyTileI, (cols_out + kCopyTileJ - 1) / kCopyTileJ);

@@ -36,6 +36,8 @@ KIND_BLOCK_CYCLIC, KIND_ROW_SHARDS, KIND_COL_SHARDS = 0, 1, 2
 # default: at 8192 on 2 B200s it measured 23.8-24.0 ms/step against 23.2-23.5 with one pull and one product --
 # under the 1 kW power cap the product slows down by what the overlap hides, and chunking adds partial waves.
 PIPELINE_GATHERS = os.environ.get("SOAP_TP_PIPELINE_GATHERS", "0") == "1"
+# SOAP_TP_DISTRIBUTED_QR=0: every factorisation runs on one leader rank even when its group has more ranks
+DISTRIBUTED_QR = os.environ.get("SOAP_TP_DISTRIBUTED_QR", "1") != "0"
 # output tiles a chunk must keep (about one wave of the 148 SMs); tests lower it to chunk small problems
 PIPELINE_MIN_TILES = max(1, int(os.environ.get("SOAP_TP_PIPELINE_MIN_TILES", "120")))
 
@@ -609,9 +611,25 @@ def _dist_gather_table(table: Tensor, src: Source, map_i: IndexMap, map_j: Index
 
 
 def qr_many(e: GridEngine, jobs) -> None:
-    """``jobs``: list of ``(packed matrix, packed Q, size, column_order)``; see :func:`_factor_on_leaders`."""
-    from ..ops.basis import count_qr_call
+    """``jobs``: list of ``(packed matrix, packed Q, size, column_order)``, factored concurrently.
 
+    With at least two ranks per job the work of each factorisation is spread over the job's ranks
+    (``engine/dist_qr.py``: panel chain on a leader, accumulation of ``Q`` on the others); with fewer ranks every
+    job runs on one leader rank (:func:`_factor_on_leaders`)."""
+    from ..ops.basis import count_qr_call
+    from . import dist_qr
+
+    if DISTRIBUTED_QR and all(workers for _, workers in (dist_qr.group_of(i, len(jobs), e.world) for i in range(len(jobs)))):
+        sources = [e.stage_packed(f"factor_in{index}", matrix, (size, size))
+                   for index, (matrix, _, size, _) in enumerate(jobs)]
+        e.comm.barrier()
+
+        def gather_input(index: int, planes: k.Planes) -> None:
+            size, order = jobs[index][2], jobs[index][3]
+            dist_gather(sources[index], IDENTITY, IndexMap(perm=order), size, size, planes=planes)
+
+        dist_qr.qr_jobs(e, jobs, gather_input)
+        return
     _factor_on_leaders(e, jobs, lambda index, dense_in, dense_out: factor.householder_qr(dense_in, dense_out))
     # the leader's factorisation counted itself; the other ranks took part in the same collective call
     for index in range(len(jobs)):
@@ -754,6 +772,10 @@ def prepare_refresh(e: GridEngine, global_shape) -> None:
         e.comm.segment(f"estimates:{size}:{e.nb}", max(1, numroc(size, e.nb, 0, e.Pc)))
         if e.rank == _leader_of(index, 2, e.world):
             qr_driver._workspace(size, e.device)
+    if DISTRIBUTED_QR:
+        from . import dist_qr
+
+        dist_qr.prepare(e, [rows, cols])
     e.packed_segment("stage", global_shape)
     e.packed_segment("middle", (cols, rows))
     from . import local

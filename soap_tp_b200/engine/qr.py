@@ -158,18 +158,28 @@ def _q_stream(device, slot: int) -> "torch.cuda.Stream":
     return _PANEL_STREAMS[key]
 
 
-def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor], slot: int, forward_q: bool = False):
-    """The blocked factorisation as a generator: yields after the launches of every panel."""
-    n = matrix.shape[0]
-    assert matrix.shape == (n, n) and Q.shape == (n, n)
-    device = matrix.device
+def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_order: Optional[Tensor], slot: int,
+                         forward_q: bool = False, publisher=None, size: Optional[int] = None, device=None):
+    """The blocked factorisation as a generator: yields after the launches of every panel.
+
+    With a ``publisher`` (``engine/dist_qr.py``) this rank only runs the panel chain and the trailing updates:
+    the reflectors ``V`` and the products ``Z_p = T_p V_p^T`` are written into the publisher's buffers, which
+    other ranks can read, ``publisher.announce(p)`` is called on the main stream once panel ``p``'s are complete,
+    and the explicit ``Q`` is accumulated elsewhere.  ``matrix=None``: the workspace planes ``C`` already hold
+    the (column-permuted) input.
+    """
+    n = matrix.shape[0] if matrix is not None else int(size)
+    device = matrix.device if matrix is not None else device
     ws = _workspace(n, device, slot)
-    C, Qp, V = ws["C"], ws["Q"], ws["V"]
-    source = matrix
-    if column_order is not None:
-        source = ws["staging"]
-        k.gather2d(matrix, source, None, column_order)
-    k.split_planes(source, out=C)
+    C, Qp = ws["C"], ws["Q"]
+    V = publisher.V if publisher is not None else ws["V"]
+    if matrix is not None:
+        assert matrix.shape == (n, n)
+        source = matrix
+        if column_order is not None:
+            source = ws["staging"]
+            k.gather2d(matrix, source, None, column_order)
+        k.split_planes(source, out=C)
     stream = k._stream
     panels = list(range(0, n, PANEL))
     main = torch.cuda.current_stream(device)
@@ -198,12 +208,18 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
             done.record(side)
         return done
 
+    def z_of(p: int) -> k.Planes:
+        bw, r = min(PANEL, n - panels[p]), n - panels[p]
+        if publisher is not None:
+            return publisher.z(p).sub(0, 0, bw, r)
+        return ws["Z"].sub(0, 0, bw, r)      # only full-width panels have columns to their right
+
     def update(p: int, first_col: int, count: int) -> None:
         """Apply the block reflector of panel ``p`` to ``count`` columns starting at ``first_col``."""
         j0 = panels[p]
         bw, r = min(PANEL, n - j0), n - j0
         v = V.sub(j0, j0, r, bw)
-        z = ws["Z"].sub(0, 0, bw, r)     # only full-width panels have columns to their right
+        z = z_of(p)
         w = ws["W"].sub(0, 0, bw, count)
         block = C.sub(j0, first_col, r, count)
         _skinny_product(ws, v, block, w)                                                    # W = V^T C
@@ -218,6 +234,7 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
     done = launch_panel(0, start)
 
     q_stream = None
+    forward_q = forward_q and publisher is None
     if forward_q:
         # Q^T lives in the planes `Qp`; every panel's reflector is applied to its rows j0.. from the left,
         # exactly like the trailing matrix, on a stream of its own with its own scratch.
@@ -245,12 +262,14 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
         nc = n - j0 - bw
         main.wait_event(done)
         panel_done = done
-        if nc > 0:
+        if nc > 0 or publisher is not None:
             vt, Tt = ws["Vt"][p], ws["Tt"][p]
             t_op = k.Planes(Tt.hi, Tt.lo, bw, bw, Tt.ld)
             vt_op = vt.sub(0, 0, bw, r)
-            z = ws["Z"].sub(0, 0, bw, r)
-            k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z, force_narrow=True)            # Z = T V^T
+            k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z_of(p), force_narrow=True)      # Z = T V^T
+            if publisher is not None:
+                publisher.announce(p)
+        if nc > 0:
             ahead = min(PANEL, nc)
             update(p, j0 + bw, ahead)
             ready = torch.cuda.Event()
@@ -261,14 +280,17 @@ def _factorisation_steps(matrix: Tensor, Q: Tensor, column_order: Optional[Tenso
         if forward_q:
             accumulate_q(p, panel_done)
         yield
+    if publisher is not None:
+        return
     if forward_q:
         finished = torch.cuda.Event()
         finished.record(q_stream)
         main.wait_event(finished)
         # planes element [c, k] of Q^T is Q[c, k]: hi + lo, read row-major, is Q itself
         row_major = ws["staging"].T
-        torch.add(Qp.hi[:n, :n], Qp.lo[:n, :n], out=row_major)
-        Q.copy_(row_major)
+        _C.planes_sum(Qp.hi.data_ptr(), Qp.lo.data_ptr(), Qp.ld, row_major.data_ptr(), n, n, n, stream())
+        k._count("planes_sum_kernel")
+        k.gather2d(row_major, Q, None, None)
         k.mark_written(Q)
         return
     # explicit Q = H_0 H_1 ... applied to the identity, last panel first

@@ -375,3 +375,26 @@ def case_redistribute_permute_subgroups(rank, world, device_kind, shape, nb):
     lr, lc = layout.local_2d_block_cyclic_shape(shape, nb, grid, local_rank)
     want = pack(full[ro][:, co], nb, grid, local_rank, device)
     assert torch.equal(X[:lr, :lc], want[:lr, :lc])
+
+
+def case_qr_properties(rank, world, device_kind, n, nb, grid, kind):
+    """``qr_2d_block_cyclic_`` on inputs that stress the factorisation: several panels, ragged last panel,
+    rank-deficient columns.  ``Q`` must be orthogonal and ``Q^T A`` upper triangular (the defining properties;
+    the factor itself is not unique when ``A`` is singular)."""
+    device = dev(device_kind, rank)
+    A0 = seeded((n, n), 60)
+    if kind == "rank_deficient":
+        A0[:, n // 3] = A0[:, 1]                # a repeated column
+        A0[:, n // 2] = 0.0                     # a zero column
+        A0[:, -5:] = A0[:, :5] @ seeded((5, 5), 61)      # the last columns depend on the first
+    elif kind == "graded":
+        A0 = A0 * torch.logspace(0, -6, n)[None, :]
+    A, Q = pack(A0, nb, grid, rank, device), pack(torch.zeros(n, n), nb, grid, rank, device)
+    ops.qr_2d_block_cyclic_(A, Q, n, nb, grid)
+    got = unpack(Q, (n, n), nb, grid).double()
+    eye = torch.eye(n, dtype=torch.float64)
+    assert float((got.T @ got - eye).abs().max()) <= 1e-4, float((got.T @ got - eye).abs().max())
+    R = got.T @ A0.double()
+    below = torch.tril(R, diagonal=-1)
+    scale = float(A0.double().norm(dim=0).max())
+    assert float(below.abs().max()) <= 2e-5 * scale * max(1.0, n ** 0.5 / 8), (float(below.abs().max()), scale)

@@ -64,6 +64,17 @@ def test_four_ranks_ops():
     run_distributed(cases.case_batch, 4, "cuda", specs)
 
 
+def test_qr_spread_over_the_ranks():
+    """Factorisations with several panels on 4 and 8 ranks: the panel chain runs on a leader rank, the explicit
+    Q is accumulated by the other ranks of the job's group and pulled into the packed layout."""
+    specs = [("case_power_iteration_qr", (700, 128, GRID4)), ("case_refresh", ((520, 390), 128, GRID4)),
+             ("case_qr_properties", (1100, 128, GRID4, "random")), ("case_qr_properties", (650, 64, GRID4, "rank_deficient")),
+             ("case_qr_properties", (384, 128, GRID4, "graded"))]
+    run_distributed(cases.case_batch, 4, "cuda", specs)
+    run_distributed(cases.case_batch, 8, "cuda", [
+        ("case_refresh", ((400, 300), 64, (2, 4))), ("case_qr_properties", (900, 128, (2, 4), "rank_deficient"))])
+
+
 def test_four_ranks_trajectory():
     specs = [("case_soap_trajectory", (shape, 2, GRID4, sd) + TINY)
              for shape in [(8, 8), (20, 20), (12, 12)] for sd in (0, 1)]

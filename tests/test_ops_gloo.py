@@ -41,6 +41,7 @@ def test_rotations_and_permutation():
 def test_power_iteration_qr_and_basis():
     specs = [("case_power_iteration_qr", (n, 2, GRID)) for n in (8, 9, 12, 13)]
     specs.append(("case_estimated_order_and_qr", (12, 2, GRID)))
+    specs += [("case_qr_properties", (24, 4, GRID, "rank_deficient")), ("case_qr_properties", (20, 4, GRID, "graded"))]
     specs += [("case_initialize_basis", (g, side, 2, GRID, "eigh")) for g, side in
               [((8, 8), "left"), ((8, 12), "right"), ((12, 8), "left"), ((9, 13), "left")]]
     specs += [("case_refresh", (shape, 2, GRID)) for shape in [(8, 8), (8, 12), (13, 9)]]
