@@ -183,7 +183,7 @@ def run(args: argparse.Namespace) -> int:
         from soap_tp_b200 import soap_step
         from soap_tp_b200.engine import kernels
 
-        basis = args.basis_implementation or "jacobi"
+        basis = args.basis_implementation or "householder"
         state: dict = {}
 
         def make_step(side: int, target: dict):
@@ -384,7 +384,7 @@ def run(args: argparse.Namespace) -> int:
             if world > 1 and side % world == 0:
                 check["side_problem_vs_single_gpu_pipeline"] = checks.side_problem_against_one_gpu(
                     lambda: make_step(side, {}), side, args.block_size, grid, args.shard_dim,
-                    steps=args.refresh_interval + 2, interval=args.refresh_interval)
+                    steps=args.refresh_interval + 2, interval=args.refresh_interval, implementation=basis)
             else:
                 check["side_problem_vs_single_gpu_pipeline"] = None    # one rank: the two paths are the same code
             kernels.check_status()

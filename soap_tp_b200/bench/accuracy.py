@@ -30,7 +30,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--rtol", type=float, default=1e-5)
     parser.add_argument("--block-cap", type=int, default=128)
-    parser.add_argument("--basis-implementations", nargs="+", default=["jacobi"])
+    parser.add_argument("--basis-implementations", nargs="+", default=["householder"])
     parser.add_argument("--basis-refresh-interval", type=int, default=2)
     parser.add_argument("--shard-dims", type=int, nargs="+", default=[0, 1])
     parser.add_argument("--device", choices=("cuda", "cpu"), default="cuda")

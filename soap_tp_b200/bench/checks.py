@@ -101,7 +101,8 @@ def gram_error(state: MutableMapping, gradients: Callable[[int], Tensor], histor
 
 
 def side_problem_against_one_gpu(step_fn_factory: Callable[[], Callable[[Tensor], Tensor]], size: int, block: int, grid,
-                                 shard_dim: int, steps: int, interval: int, scale: float = 1e-2) -> Dict[str, float]:
+                                 shard_dim: int, steps: int, interval: int, scale: float = 1e-2,
+                                 implementation: str = "householder") -> Dict[str, float]:
     """Run ``steps`` calls on a ``size x size`` parameter through the distributed path (``step_fn_factory()``
     returns a fresh ``step(shard) -> update shard``) and, on every rank, through the single-GPU pipeline with
     the full gradient; report the worst relative L2 distance of the updates and the step it occurred at."""
@@ -129,7 +130,7 @@ def side_problem_against_one_gpu(step_fn_factory: Callable[[], Callable[[Tensor]
             for name, buffer_shape in state_shapes(shape).items():
                 single[name] = empty_2d_block_cyclic_like_shape(*buffer_shape, device=device, zero=True)
         expected = local.soap_step(full, single, global_shape=shape, beta=0.95, beta1=0.95, beta2=0.95, eps=1e-8,
-                                   interval=interval, implementation="jacobi", initializing=initializing)
+                                   interval=interval, implementation=implementation, initializing=initializing)
         if index == 0:
             continue
         distance = float((gathered - expected).norm() / expected.norm())

@@ -46,23 +46,32 @@ def gather_case(args) -> int:
     from ..engine import kernels as k
     from ..parallel.comm import get_communicator
 
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", device_id=device)
-    if dist.get_world_size() != 2:
-        raise SystemExit("the gather case needs exactly two ranks")
-    rank = dist.get_rank()
-    comm = get_communicator(device)
     n, nb, virtual, Pr, Pc = args.size, 128, 8, 2, 4
     shard = n * n // virtual
-    segment = comm.segment("gather_case", virtual * shard)
-    segment.local.normal_()
-    comm.barrier()
-    # virtual rank 0's data is mine, virtual ranks 1..7 live in the partner's segment
-    partner = segment.peer_ptrs[1 - rank]
-    table = torch.tensor([segment.peer_ptrs[rank]] + [partner + 4 * v * shard for v in range(1, virtual)],
-                         dtype=torch.int64, device=device)
+    single = "WORLD_SIZE" not in os.environ or int(os.environ["WORLD_SIZE"]) == 1
+    if single:
+        # one process, one GPU: all eight "ranks" are slices of one local buffer (what an ncu capture can run;
+        # the figures then are those of the kernel against local HBM, not against NVLink)
+        device = torch.device("cuda", torch.cuda.current_device())
+        rank, comm = 0, None
+        buffer = torch.randn(virtual * shard, device=device)
+        table = torch.tensor([buffer.data_ptr() + 4 * v * shard for v in range(virtual)], dtype=torch.int64, device=device)
+    else:
+        local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+        dist.init_process_group("nccl", device_id=device)
+        if dist.get_world_size() != 2:
+            raise SystemExit("the gather case needs one rank (local memory) or exactly two ranks")
+        rank = dist.get_rank()
+        comm = get_communicator(device)
+        segment = comm.segment("gather_case", virtual * shard)
+        segment.local.normal_()
+        comm.barrier()
+        # virtual rank 0's data is mine, virtual ranks 1..7 live in the partner's segment
+        partner = segment.peer_ptrs[1 - rank]
+        table = torch.tensor([segment.peer_ptrs[rank]] + [partner + 4 * v * shard for v in range(1, virtual)],
+                             dtype=torch.int64, device=device)
     planes = k.Planes.empty(n, n // Pr, device)
     stream = lambda: torch.cuda.current_stream().cuda_stream
 
@@ -79,16 +88,18 @@ def gather_case(args) -> int:
             k._C.force_scalar_gather(scalar)
             us = timed(lambda: pull(kind, cols_out, jP, transpose), args.repeats)
             best = torch.tensor([us], device=device)
-            dist.all_reduce(best, op=dist.ReduceOp.MAX)
+            if not single:
+                dist.all_reduce(best, op=dist.ReduceOp.MAX)
             if rank == 0:
                 bytes_read = 4.0 * n * cols_out
                 print(f"{name}: {'element-wise' if scalar else '16-byte'} {float(best):.1f} us, "
                       f"{bytes_read / float(best) / 1e3:.0f} GB/s of source bytes ({bytes_read * 7 / 8 / float(best) / 1e3:.0f} "
                       f"GB/s over NVLink), {3 * bytes_read / float(best) / 1e6:.2f} TB/s of local traffic incl. both planes")
         k._C.force_scalar_gather(False)
-    comm.barrier()
     k.check_status()
-    dist.destroy_process_group()
+    if not single:
+        comm.barrier()
+        dist.destroy_process_group()
     return 0
 
 

@@ -36,7 +36,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--block-size", type=int, default=128)
     parser.add_argument("--shard-dim", type=int, choices=(0, 1), default=0)
-    parser.add_argument("--basis-implementation", default="jacobi")
+    parser.add_argument("--basis-implementation", default="householder")
     parser.add_argument("--basis-refresh-interval", type=int, default=10)
     parser.add_argument("--seed", type=int, default=42)
     parser.add_argument("--device", choices=("cuda", "cpu"), default="cuda")

@@ -60,6 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
               "--expt-relaxed-constexpr", *ARCH_FLAGS, *_includes()]
     if os.environ.get("SOAP_GEMM_BK"):
         common += [f"-DSOAP_GEMM_BK={int(os.environ['SOAP_GEMM_BK'])}"]
+    if os.environ.get("SOAP_GEMM_TERMS"):
+        common += [f"-DSOAP_GEMM_TERMS={int(os.environ['SOAP_GEMM_TERMS'])}"]     # timing experiments (see gemm_tf32x3.cu)
     if os.environ.get("SOAP_QR_TRACE", "0") == "1":
         common += ["-DSOAP_QR_TRACE"]     # clock64 stamps in the one-column QR panel kernel (kernel_cases --trace)
     if verbose:

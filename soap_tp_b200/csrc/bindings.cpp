@@ -14,6 +14,7 @@
 #include "gemm.h"
 #include "jacobi.h"
 #include "qr.h"
+#include "tridiag.h"
 
 namespace py = pybind11;
 using namespace soapb200;
@@ -156,6 +157,27 @@ PYBIND11_MODULE(_C, m) {
   m.def("planes_sum", [](uint64_t hi, uint64_t lo, int64_t ldp, uint64_t out, int64_t ldo, int depth, int cols, uint64_t stream) {
     planes_sum(ptr<const float>(hi), ptr<const float>(lo), ldp, ptr<float>(out), ldo, depth, cols, stream_of(stream));
   });
+  m.def("sytrd_panel",
+        [](uint64_t A, int64_t lda, int n, int j0, int nb, uint64_t vw, uint64_t x, uint64_t y, uint64_t partial, uint64_t d,
+           uint64_t e, uint64_t tau, uint64_t za_hi, uint64_t za_lo, uint64_t zb_hi, uint64_t zb_lo, uint64_t v_hi,
+           uint64_t v_lo, int64_t ldv, uint64_t vt_hi, uint64_t vt_lo, int64_t ldvt, uint64_t t_hi, uint64_t t_lo,
+           uint64_t tt_hi, uint64_t tt_lo, int64_t ldt, uint64_t barrier, uint64_t status, int last, uint64_t stream) {
+          SytrdPanelArgs args{ptr<float>(A), lda, n, j0, nb, ptr<float>(vw), ptr<float>(x), ptr<float>(y), ptr<float>(partial),
+                              ptr<double>(d), ptr<double>(e), ptr<float>(tau), ptr<float>(za_hi), ptr<float>(za_lo),
+                              ptr<float>(zb_hi), ptr<float>(zb_lo), ptr<float>(v_hi), ptr<float>(v_lo), ldv, ptr<float>(vt_hi),
+                              ptr<float>(vt_lo), ldvt, ptr<float>(t_hi), ptr<float>(t_lo), ptr<float>(tt_hi), ptr<float>(tt_lo),
+                              ldt, ptr<unsigned int>(barrier), ptr<int>(status), last};
+          sytrd_panel(args, stream_of(stream));
+        });
+  m.def("tridiagonal_bisect", [](uint64_t d, uint64_t e, int n, double lo, double hi, double pivmin, uint64_t lambda, uint64_t stream) {
+    tridiagonal_bisect(ptr<const double>(d), ptr<const double>(e), n, lo, hi, pivmin, ptr<double>(lambda), stream_of(stream));
+  });
+  m.def("tridiagonal_vectors", [](uint64_t d, uint64_t e, int n, uint64_t lambda, double pivmin, uint64_t lplus, uint64_t dplus,
+                                  uint64_t uminus, uint64_t z, uint64_t stream) {
+    tridiagonal_vectors(ptr<const double>(d), ptr<const double>(e), n, ptr<const double>(lambda), pivmin, ptr<double>(lplus),
+                        ptr<double>(dplus), ptr<double>(uminus), ptr<float>(z), stream_of(stream));
+  });
+  m.attr("TRIDIAG_PANEL") = kTridiagPanel;
   m.attr("QR_PANEL_WIDTH") = kQrPanelWidth;
   m.attr("QR_ROWS_PER_CTA") = kQrRowsPerCta;
   m.attr("QR_MAX_ROWS") = kQrMaxRows;

@@ -46,6 +46,11 @@ constexpr int kBM = 128;
 // deeper pipeline of the 64-byte variant did not help (4.23 ms against 4.15 ms), because the kernel
 // is bound by the L2 -> shared-memory traffic of the four operand planes, not by load latency.
 constexpr int kBK = SOAP_GEMM_BK;
+// Timing experiments only: SOAP_GEMM_TERMS < 3 drops correction products (wrong results, same data movement), which
+// tells how much of the kernel's time is tensor-pipe time and how much is operand traffic.
+#ifndef SOAP_GEMM_TERMS
+#define SOAP_GEMM_TERMS 3
+#endif
 static_assert(kBK == 16 || kBK == 32, "one swizzle row per k-block: 64 or 128 bytes");
 constexpr int kRowBytes = kBK * 4;
 constexpr int kEpiWarps = 8;     // two warps per TMEM lane quarter, each owning half of the tile's columns
@@ -435,10 +440,16 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
         for (int k = 0; k < kBK / 8; ++k) {
           const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);  // 8 tf32 = 32 bytes along the swizzle row
           // small terms first, the dominant hi*hi product last
+#if SOAP_GEMM_TERMS >= 3
           umma_tf32_ss(tmem_acc, a_lo + adv, b_hi + adv, idesc, first ? 0u : 1u);
           first = 0;
-          umma_tf32_ss(tmem_acc, a_hi + adv, b_lo + adv, idesc, 1);
-          umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+#endif
+#if SOAP_GEMM_TERMS >= 2
+          umma_tf32_ss(tmem_acc, a_hi + adv, b_lo + adv, idesc, first ? 0u : 1u);
+          first = 0;
+#endif
+          umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, first ? 0u : 1u);
+          first = 0;
         }
         umma_commit(&empty_bar[s]);  // stage reusable once these UMMAs have read it
       }

@@ -14,6 +14,7 @@ enum StatusCode : int {
   kStatusBadArgument = 5,
   kStatusPanelExchangeTimeout = 6,    // QR panel: a poll of the exchange between its thread blocks ran out
   kStatusPeerFlagTimeout = 7,         // a wait for a peer's "data ready" flag ran out
+  kStatusGridBarrierTimeout = 8,      // tridiagonalisation: a barrier over the CTAs of the launch ran out
 };
 
 }  // namespace soapb200

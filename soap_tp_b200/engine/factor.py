@@ -33,7 +33,16 @@ def householder_qr_pair(jobs) -> None:
 
 
 def symmetric_eigenbasis(P: Tensor, Q: Tensor, work: Tensor, values: Tensor, implementation: str) -> Tensor:
-    """Eigenvectors of symmetric ``P`` into ``Q`` and eigenvalues into ``values``, both descending."""
-    from . import jacobi
+    """Eigenvectors of symmetric ``P`` into ``Q`` and eigenvalues into ``values``, both descending.
 
-    return jacobi.symmetric_eigenbasis(P, Q, work, values)
+    ``"jacobi"`` runs the two-sided block-Jacobi solver (``engine/jacobi.py``); every other accepted name
+    (``"householder"``, and the reference's ``"elpa"`` and ``"eigh"``) runs Householder tridiagonalisation,
+    bisection and twisted factorisation with back-transformation (``engine/tridiag.py``) -- the method of the
+    reference's ELPA default (``src/soap_tp/ops/factorizations.py:472-547``)."""
+    if implementation == "jacobi":
+        from . import jacobi
+
+        return jacobi.symmetric_eigenbasis(P, Q, work, values)
+    from . import tridiag
+
+    return tridiag.symmetric_eigenbasis(P, Q, work, values)

@@ -33,6 +33,7 @@ STATUS_MESSAGES = {
     5: "bad kernel argument",
     6: "QR panel exchange between thread blocks timed out",
     7: "wait for a peer's data-ready flag timed out",
+    8: "tridiagonalisation grid barrier timed out",
 }
 
 LAUNCH_COUNTS: Dict[str, int] = {}

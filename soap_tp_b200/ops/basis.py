@@ -13,10 +13,10 @@ The reference reaches SLATE (GEMM, ``geqrf``/``unmqr``) and ELPA (fp64 one-stage
 through two pybind11 modules.  Here the CUDA path uses this package's own sm_100a kernels: the
 3xTF32 tcgen05 GEMM for ``P Q`` with the column-dot epilogue, a blocked Householder QR whose
 panel is factored by a cooperative kernel and whose trailing updates are tensor-core GEMMs, and
-a one-sided block-Jacobi symmetric eigensolver.  ``implementation`` accepts the reference's
-names (``"elpa"``, ``"eigh"``) plus ``"jacobi"``; on CPU tensors every name resolves to
-LAPACK ``torch.linalg.eigh`` on rank 0 followed by a broadcast, as ``"eigh"`` does in the
-reference.
+two symmetric eigensolvers: Householder tridiagonalisation with bisection and twisted factorisation
+(``"householder"``, and the reference's names ``"elpa"`` and ``"eigh"``) and two-sided block Jacobi
+(``"jacobi"``).  On CPU tensors every name resolves to LAPACK ``torch.linalg.eigh`` on rank 0 followed by a
+broadcast, as ``"eigh"`` does in the reference.
 """
 from __future__ import annotations
 
@@ -28,7 +28,8 @@ from torch import Tensor
 
 from . import _hostpath as host
 from .permute import permute_2d_block_cyclic_
-from .rotate import rotate_2d_block_cyclic_, validate_float_buffer, validate_world
+from .rotate import _synchronize, rotate_2d_block_cyclic_, validate_float_buffer, validate_world
+from ..layout import local_2d_block_cyclic_shape
 from ..parallel.guard import check_collective
 
 BASIS_IMPLEMENTATIONS = ("elpa", "eigh", "jacobi", "householder")
@@ -78,11 +79,20 @@ def estimated_eigenvalue_order_2d_block_cyclic_(
         raise ValueError("preconditioner, Q, and work must not overlap.")
     if not (preconditioner.stride(1) == Q.stride(1) == work.stride(1)):
         raise ValueError("preconditioner, Q, and work LDAs must match.")
+    grid = process_grid_shape
+    if slate_binding is not None:
+        # the injected binding forms work = P Q (src/soap_tp/ops/factorizations.py:235-244); the estimates follow
+        _synchronize(preconditioner.device)
+        slate_binding.slate_symmetric_multiply_float(preconditioner.data_ptr(), Q.data_ptr(), work.data_ptr(), size,
+                                                     preconditioner.stride(1), block_size, grid[0], grid[1])
+        _synchronize(preconditioner.device)
+        Qf = host.gather_block_cyclic(Q.cpu(), (size, size), block_size, grid)
+        W = host.gather_block_cyclic(work.cpu(), (size, size), block_size, grid)
+        return _stable_descending_order((Qf * W).sum(dim=0)).to(preconditioner.device)
     if preconditioner.is_cuda:
         from ..engine import api as engine
 
         return engine.estimated_order(preconditioner, Q, work, size, block_size, process_grid_shape)
-    grid = process_grid_shape
     P = host.gather_block_cyclic(preconditioner, (size, size), block_size, grid)
     Qf = host.gather_block_cyclic(Q, (size, size), block_size, grid)
     W = P @ Qf
@@ -114,6 +124,13 @@ def qr_2d_block_cyclic_(
         raise ValueError("matrix and Q must share a device.")
     if matrix.data_ptr() == Q.data_ptr():
         raise ValueError("matrix and Q must not overlap.")
+    if slate_binding is not None:
+        count_qr_call()
+        _synchronize(matrix.device)
+        slate_binding.slate_qr_float(matrix.data_ptr(), Q.data_ptr(), size, matrix.stride(1), Q.stride(1), block_size,
+                                     process_grid_shape[0], process_grid_shape[1])
+        _synchronize(matrix.device)
+        return Q
     if matrix.is_cuda:
         from ..engine import api as engine
 
@@ -138,7 +155,7 @@ def power_iteration_qr_2d_block_cyclic_(
 ) -> Tensor:
     """One power iteration: sort ``P Q`` by estimated eigenvalue, QR it into ``Q``; returns the order."""
     check_collective("power_iteration_qr_2d_block_cyclic_", size, block_size, tuple(process_grid_shape))
-    if preconditioner.is_cuda:
+    if preconditioner.is_cuda and slate_binding is None:
         # Validation happens inside the two public ops on the host path; the fused device path
         # validates once and folds the column permutation into the QR's panel gather.
         rank, _ = validate_world(process_grid_shape)
@@ -150,11 +167,11 @@ def power_iteration_qr_2d_block_cyclic_(
 
         return engine.power_iteration_qr(preconditioner, Q, work, size, block_size, process_grid_shape)
     order = estimated_eigenvalue_order_2d_block_cyclic_(
-        preconditioner, Q, work, size, block_size, process_grid_shape
+        preconditioner, Q, work, size, block_size, process_grid_shape, slate_binding=slate_binding
     )
     identity = torch.arange(size, dtype=torch.int64, device=work.device)
     permute_2d_block_cyclic_(work, (size, size), identity, order, block_size, process_grid_shape)
-    qr_2d_block_cyclic_(work, Q, size, block_size, process_grid_shape)
+    qr_2d_block_cyclic_(work, Q, size, block_size, process_grid_shape, slate_binding=slate_binding)
     return order
 
 
@@ -200,6 +217,23 @@ def initialize_basis_2d_block_cyclic_(
         raise ValueError("eigenvalues must be contiguous.")
     if eigenvalues.device != preconditioner.device:
         raise ValueError("eigenvalues must share the matrix device.")
+    if elpa_binding is not None and implementation == "elpa":
+        # An injected eigensolver with the reference's entry point: fp64 copies, -A so that its ascending order
+        # is the descending order of A (src/soap_tp/ops/factorizations.py:495-546)
+        local_rows, local_columns = local_2d_block_cyclic_shape((size, size), block_size, process_grid_shape, rank)
+        work.copy_(preconditioner).neg_()
+        work64 = torch.empty_strided(work.size(), work.stride(), dtype=torch.float64, device=work.device).copy_(work)
+        Q64 = torch.empty_strided(Q.size(), Q.stride(), dtype=torch.float64, device=Q.device)
+        values64 = torch.empty_like(eigenvalues, dtype=torch.float64)
+        gpu_id = -1 if not preconditioner.is_cuda else (preconditioner.device.index or 0)
+        _synchronize(preconditioner.device)
+        elpa_binding.elpa_eigenvectors_2d_block_cyclic_double(
+            work64.data_ptr(), values64.data_ptr(), Q64.data_ptr(), size, local_rows, local_columns, block_size,
+            process_grid_shape[0], process_grid_shape[1], gpu_id)
+        _synchronize(preconditioner.device)
+        Q.copy_(Q64)
+        eigenvalues.copy_(values64).neg_()
+        return Q
     if preconditioner.is_cuda:
         from ..engine import api as engine
 
@@ -243,15 +277,16 @@ def refresh_bases_and_transport_optimizer_state_(
     check_collective("refresh_bases_and_transport_optimizer_state_", tuple(global_shape), block_size, tuple(process_grid_shape))
     rows, columns = global_shape
     grid = process_grid_shape
-    rotate_2d_block_cyclic_(momentum, Q_left, Q_right, global_shape, block_size, grid, direction="backward")
+    injected = dict(slate_binding=slate_binding)
+    rotate_2d_block_cyclic_(momentum, Q_left, Q_right, global_shape, block_size, grid, direction="backward", **injected)
     left_order = power_iteration_qr_2d_block_cyclic_(
-        left_preconditioner, Q_left, left_work, rows, block_size, grid
+        left_preconditioner, Q_left, left_work, rows, block_size, grid, **injected
     )
     right_order = power_iteration_qr_2d_block_cyclic_(
-        right_preconditioner, Q_right, right_work, columns, block_size, grid
+        right_preconditioner, Q_right, right_work, columns, block_size, grid, **injected
     )
     permute_2d_block_cyclic_(variance, global_shape, left_order, right_order, block_size, grid)
-    rotate_2d_block_cyclic_(momentum, Q_left, Q_right, global_shape, block_size, grid, direction="forward")
+    rotate_2d_block_cyclic_(momentum, Q_left, Q_right, global_shape, block_size, grid, direction="forward", **injected)
     return left_order, right_order
 
 

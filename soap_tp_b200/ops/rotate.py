@@ -38,6 +38,12 @@ def validate_float_buffer(name: str, matrix: Tensor, global_shape, block_size: i
 
 
 @torch.no_grad()
+def _synchronize(device: torch.device) -> None:
+    """An injected binding works on raw pointers outside torch's stream ordering."""
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+
+
 def rotate_2d_block_cyclic_(
     matrix: Tensor,
     Q_left: Tensor,
@@ -51,8 +57,9 @@ def rotate_2d_block_cyclic_(
 ) -> Tensor:
     """Rotate a packed matrix in place and return it.
 
-    ``slate_binding`` is accepted for call-site compatibility with the reference and ignored:
-    there is no external GEMM library behind this op.
+    ``slate_binding``: an object with the reference's ``slate_forward_rotation_float`` /
+    ``slate_backward_rotation_float`` entry points; when given it is called (pointer-level convention of
+    ``src/soap_tp/ops/factorizations.py:162-182``) instead of the built-in path.
     """
     check_collective("rotate_2d_block_cyclic_", tuple(global_shape), block_size, tuple(process_grid_shape), direction)
     if direction not in {"forward", "backward"}:
@@ -66,6 +73,14 @@ def rotate_2d_block_cyclic_(
         raise ValueError("matrix and bases must share a device.")
     if len({matrix.data_ptr(), Q_left.data_ptr(), Q_right.data_ptr()}) != 3:
         raise ValueError("matrix and basis buffers must not overlap.")
+    if slate_binding is not None:
+        function = (slate_binding.slate_forward_rotation_float if direction == "forward"
+                    else slate_binding.slate_backward_rotation_float)
+        _synchronize(matrix.device)
+        function(Q_left.data_ptr(), matrix.data_ptr(), Q_right.data_ptr(), rows, columns, Q_left.stride(1),
+                 matrix.stride(1), Q_right.stride(1), block_size, process_grid_shape[0], process_grid_shape[1])
+        _synchronize(matrix.device)
+        return matrix
     if matrix.is_cuda:
         from ..engine import api as engine
 
@@ -78,4 +93,4 @@ def rotate_2d_block_cyclic_(
     return host.store_block_cyclic_(matrix, Y, global_shape, block_size, grid)
 
 
-__all__ = ["rotate_2d_block_cyclic_", "validate_float_buffer", "validate_world"]
+__all__ = ["rotate_2d_block_cyclic_", "validate_float_buffer", "validate_world", "_synchronize"]

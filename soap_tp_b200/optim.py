@@ -11,7 +11,11 @@ weight in the same order on every rank, then apply learning rate and weight deca
   exactly the reference's keys (``left_preconditioner`` ... ``variance``, ``step``);
 * replicated 2-D parameters are sharded on the fly (each rank preconditions a slice of the
   gradient, the update shards are all-gathered);
-* everything else (1-D parameters, matrices with a side above ``max_precond_dim`` or with no side
+* a tensor-parallel matrix whose SHARDED side exceeds ``max_precond_dim`` (vocabulary-sized embeddings and
+  heads) is preconditioned on its other side only, with the identity as the long side's basis, as original SOAP
+  does (``tests/reference/soap.py:363-367`` of the reference); on CUDA that one-sided update is local to a rank
+  apart from one all-reduce (``engine/one_sided.py``);
+* everything else (1-D parameters, other matrices with a side above ``max_precond_dim`` or with no side
   divisible by the world size) gets AdamW;
 * decoupled weight decay and the learning rate are applied here.
 
@@ -44,7 +48,7 @@ class SoapTP(torch.optim.Optimizer):
         precondition_frequency: int = 10,
         block_size: int = 128,
         process_grid_shape: Optional[Tuple[int, int]] = None,
-        basis_implementation: str = "jacobi",
+        basis_implementation: str = "householder",
         max_precond_dim: int = 16384,
         adamw_betas: Tuple[float, float] = (0.9, 0.95),
     ) -> None:
@@ -80,7 +84,13 @@ class SoapTP(torch.optim.Optimizer):
                 plan = dict(global_shape=(rows, cols), shard_dim=1, replicated=True)
             else:
                 return None
-        if max(plan["global_shape"]) > group["max_precond_dim"]:
+        limit = group["max_precond_dim"]
+        if max(plan["global_shape"]) > limit:
+            long_side = 0 if plan["global_shape"][0] > limit else 1
+            short_fits = plan["global_shape"][1 - long_side] <= limit
+            if (p.is_cuda and not plan["replicated"] and long_side == plan["shard_dim"] and short_fits):
+                plan["one_sided"] = True       # the sharded side keeps the identity basis
+                return plan
             return None
         return plan
 
@@ -105,6 +115,21 @@ class SoapTP(torch.optim.Optimizer):
                     continue
                 state = self.state[p]
                 gradient = p.grad
+                if plan.get("one_sided"):
+                    from .engine import one_sided
+
+                    # the engine works on row shards; a column-sharded long side is the same problem transposed
+                    rows_sharded = plan["shard_dim"] == 0
+                    update = one_sided.step(
+                        gradient if rows_sharded else gradient.T, state, beta=group["shampoo_beta"],
+                        beta1=group["betas"][0], beta2=group["betas"][1], eps=group["eps"],
+                        interval=group["precondition_frequency"], implementation=group["basis_implementation"])
+                    if not rows_sharded:
+                        update = update.T
+                    if wd != 0.0:
+                        p.mul_(1.0 - lr * wd)
+                    p.add_(update.to(p.dtype), alpha=-lr)
+                    continue
                 if plan["replicated"] and world > 1:
                     gradient = gradient.chunk(world, dim=plan["shard_dim"])[rank].contiguous()
                 update = soap_step(
@@ -149,7 +174,7 @@ class SoapTP(torch.optim.Optimizer):
         for group in self.param_groups:
             for p in group["params"]:
                 plan = self._plan(p, group)
-                if plan is not None and "left_basis" in self.state.get(p, {}):
+                if plan is not None and not plan.get("one_sided") and "left_basis" in self.state.get(p, {}):
                     layouts[index] = dict(global_shape=list(plan["global_shape"]), shard_dim=plan["shard_dim"],
                                           block_size=group["block_size"], grid=list(self.grid))
                 index += 1
@@ -164,10 +189,16 @@ class SoapTP(torch.optim.Optimizer):
         saved_state = state_dict["state"]
         # AdamW-style entries go through the stock loader; packed SOAP buffers are restored by hand
         # because the stock loader would cast them to the parameter dtype and drop their strides.
-        stock = {k: v for k, v in saved_state.items() if "left_basis" not in v}
+        stock = {k: v for k, v in saved_state.items() if "right_basis" not in v}
         super().load_state_dict({"state": stock, "param_groups": state_dict["param_groups"]})
         for index, entry in saved_state.items():
+            if "right_basis" not in entry:
+                continue
             if "left_basis" not in entry:
+                # one-sided state: fp32 buffers of this rank, restored with their strides
+                p = params[int(index)]
+                self.state[p] = {name: (value.to(device=p.device, dtype=torch.float32).clone(memory_format=torch.preserve_format)
+                                        if torch.is_tensor(value) else value) for name, value in entry.items()}
                 continue
             p, group = params[int(index)], groups[int(index)]
             plan = self._plan(p, group)
@@ -202,6 +233,9 @@ class SoapTP(torch.optim.Optimizer):
         local = sys.modules.get("soap_tp_b200.engine.local")
         if local is not None:
             local._CONTEXTS.clear()
+        one_sided = sys.modules.get("soap_tp_b200.engine.one_sided")
+        if one_sided is not None:
+            one_sided._PLANES.clear()
         distributed = sys.modules.get("soap_tp_b200.engine.distributed")
         if distributed is not None:
             for engine in distributed._ENGINES.values():

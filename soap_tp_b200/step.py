@@ -93,9 +93,10 @@ def soap_step(
 ) -> Tensor:
     """Run one SOAP update for a row- (``shard_dim=0``) or column- (``shard_dim=1``) sharded gradient.
 
-    Returns a new fp32 tensor shaped like ``gradient_shard``.  ``elpa_binding`` and
-    ``slate_binding`` are accepted so call sites written for the reference keep working; no
-    external library is involved and they are ignored.
+    Returns a new fp32 tensor shaped like ``gradient_shard``.  ``slate_binding`` / ``elpa_binding``: objects with
+    the reference's native entry points (``soap_tp_b200.bindings`` has this package's own); when given, the step
+    is composed from the public ops and every rotation, ``P Q`` product, QR and (for ``"elpa"``) eigensolve goes
+    through the injected object, as in the reference (``src/soap_tp/soap.py:139-141``).
     """
     if basis_refresh_interval <= 0:
         raise ValueError("basis_refresh_interval must be positive.")
@@ -119,7 +120,8 @@ def soap_step(
     profile_step = 0 if initializing else int(state["step"]) + 1
     tracing = profile_enabled(profile_step)
 
-    if device.type == "cuda" and not tracing:
+    injected = slate_binding is not None or elpa_binding is not None
+    if device.type == "cuda" and not tracing and not injected:
         from .engine import api as engine
 
         return engine.soap_step(
@@ -158,14 +160,14 @@ def soap_step(
             initialize_basis_2d_block_cyclic_(
                 state["left_preconditioner"], state["left_basis"], state["left_work"],
                 torch.empty(rows, dtype=torch.float32, device=device),
-                rows, block_size, grid, implementation=basis_implementation,
+                rows, block_size, grid, implementation=basis_implementation, elpa_binding=elpa_binding,
             )
         _tap_state(["left_basis"], profile_step, state, global_shape, block_size, grid)
         with timer.stage("basis_init", device):
             initialize_basis_2d_block_cyclic_(
                 state["right_preconditioner"], state["right_basis"], state["right_work"],
                 torch.empty(columns, dtype=torch.float32, device=device),
-                columns, block_size, grid, implementation=basis_implementation,
+                columns, block_size, grid, implementation=basis_implementation, elpa_binding=elpa_binding,
             )
         _tap_state(["right_basis"], profile_step, state, global_shape, block_size, grid)
         state["step"] = 0
@@ -188,7 +190,7 @@ def soap_step(
     with timer.stage("rotate_forward", device):
         rotate_2d_block_cyclic_(
             packed, state["left_basis"], state["right_basis"], global_shape, block_size, grid,
-            direction="forward",
+            direction="forward", slate_binding=slate_binding,
         )
     profile_block_cyclic("projected_gradient", profile_step, packed, global_shape, block_size, grid)
     with timer.stage("adam", device):
@@ -201,7 +203,7 @@ def soap_step(
     with timer.stage("rotate_backward", device):
         rotate_2d_block_cyclic_(
             packed_update, state["left_basis"], state["right_basis"], global_shape, block_size, grid,
-            direction="backward",
+            direction="backward", slate_binding=slate_binding,
         )
     profile_block_cyclic("backrotated_update", profile_step, packed_update, global_shape, block_size, grid)
     with timer.stage("redistribute_out", device):
@@ -229,7 +231,7 @@ def soap_step(
                 state["left_preconditioner"], state["right_preconditioner"],
                 state["left_basis"], state["right_basis"],
                 state["left_work"], state["right_work"],
-                global_shape, block_size, grid,
+                global_shape, block_size, grid, slate_binding=slate_binding,
             )
     _tap_state(["left_basis", "right_basis", "momentum", "variance"], profile_step, state, global_shape, block_size, grid, "_after_step")
     state["step"] = step

@@ -35,7 +35,7 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--block-size", type=int, default=128)
     parser.add_argument("--precondition-frequency", type=int, default=10)
     parser.add_argument("--max-precond-dim", type=int, default=16384)
-    parser.add_argument("--basis-implementation", default="jacobi")
+    parser.add_argument("--basis-implementation", default="householder")
     parser.add_argument("--device", choices=("cuda", "cpu"), default="cuda")
     parser.add_argument("--seed", type=int, default=0)
     return parser.parse_args(argv)

@@ -1,6 +1,7 @@
 """``SoapTP`` optimizer wrapper and the tensor-parallel Llama model on CPU ranks (gloo)."""
 import io
 
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -104,3 +105,60 @@ def test_soap_tp_optimizer_two_ranks():
 
 def test_llama_tp_two_ranks():
     run_distributed(_model_case, 2)
+
+
+def _one_sided_case(rank, world):
+    """A row-sharded matrix whose sharded side is above ``max_precond_dim``: ``SoapTP`` preconditions the other
+    side only.  Float64 restatement of one-sided SOAP (identity basis on the long side) on every rank."""
+    import torch.distributed as dist
+
+    from soap_tp_b200.optim import SoapTP
+
+    device = torch.device("cuda", rank % torch.cuda.device_count())
+    rows_local, h, steps, interval = 24, 16, 6, 2
+    beta, b1, b2, eps = 0.9, 0.8, 0.9, 1e-8
+    weight = torch.nn.Parameter(torch.zeros(rows_local, h, device=device))
+    weight.tp_shard_dim, weight.tp_global_shape = 0, (rows_local * world, h)
+    optimizer = SoapTP([weight], lr=1.0, weight_decay=0.0, betas=(b1, b2), shampoo_beta=beta, eps=eps,
+                       precondition_frequency=interval, max_precond_dim=20, basis_implementation="householder")
+    assert optimizer._plan(weight, optimizer.param_groups[0]).get("one_sided")
+    full = lambda t: torch.randn(rows_local * world, h, generator=torch.Generator().manual_seed(40 + t), dtype=torch.float64)
+    R = Q = M = V = None
+    expected = torch.zeros(rows_local * world, h, dtype=torch.float64)
+    for t in range(steps):
+        G = full(t)
+        weight.grad = G[rank * rows_local:(rank + 1) * rows_local].float().to(device)
+        optimizer.step()
+        if t == 0:
+            R = (1 - beta) * G.T @ G
+            Q = torch.linalg.eigh(R)[1].flip(1)
+            M, V = torch.zeros_like(G), torch.zeros_like(G)
+            continue
+        Y = G @ Q
+        M = b1 * M + (1 - b1) * Y
+        V = b2 * V + (1 - b2) * Y * Y
+        U = (M / (1 - b1**t)) / ((V.sqrt() + eps) / (1 - b2**t) ** 0.5)
+        expected -= U @ Q.T
+        R = beta * R + (1 - beta) * G.T @ G
+        if t % interval == 0:
+            Mp = M @ Q.T
+            order = torch.argsort(((Q * (R @ Q)).sum(0)), descending=True, stable=True)
+            Qn = torch.linalg.qr((R @ Q)[:, order])[0]
+            M, V, Q = Mp @ Qn, V[:, order], Qn
+    got = weight.detach().double().cpu()
+    want = expected[rank * rows_local:(rank + 1) * rows_local]
+    error = float((got - want).norm() / want.norm())
+    assert error < 2e-4, error
+    # checkpoint round trip keeps the fp32 buffers bit for bit
+    saved = optimizer.state_dict()
+    fresh = SoapTP([weight], lr=1.0, weight_decay=0.0, max_precond_dim=20)
+    fresh.load_state_dict(saved)
+    for name in ("right_preconditioner", "right_basis", "momentum", "variance"):
+        assert torch.equal(fresh.state[weight][name], optimizer.state[weight][name])
+    dist.barrier()
+
+
+@pytest.mark.gpu
+def test_one_sided_soap_for_a_long_sharded_side():
+    run_distributed(_one_sided_case, 1)
+    run_distributed(_one_sided_case, 2)

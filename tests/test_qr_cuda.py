@@ -1,7 +1,7 @@
 """Blocked Householder QR on the GPU against its defining properties (fp64 checks).
 
-The reference tests its QR through ``power_iteration_qr`` on tiny sizes
-(``tests/test_gpu_ops.py``); here the factorisation kernel chain itself is exercised on sizes that
+The reference tests its QR binding on sizes 8 to 13 against ``numpy.linalg.qr``
+(``tests/unit/test_slate_bindings.py:244-323``); here the factorisation kernel chain itself is exercised on sizes that
 span several panels, ragged last panels, a rank-deficient input, and the concurrent two-job driver.
 """
 import pytest
