@@ -112,6 +112,7 @@ def main(argv=None) -> int:
     parser.add_argument("--repeats", type=int, default=3)
     parser.add_argument("--pairs", action="store_true", help="panel: the two-columns-per-exchange kernel")
     parser.add_argument("--rows-per-cta", type=int, default=256, choices=(128, 256), help="panel --pairs: CTA height")
+    parser.add_argument("--mixed", action="store_true", help="gemm: operands as mixed planes (bf16 correction products)")
     parser.add_argument("--trace", action="store_true",
                         help="panel: print clock64 stamps of one column step (needs a library built with SOAP_QR_TRACE=1)")
     args = parser.parse_args(argv)
@@ -126,23 +127,24 @@ def main(argv=None) -> int:
     generator = torch.Generator(device=device).manual_seed(0)
     rand = lambda *shape: torch.randn(*shape, generator=generator, device=device)
     if args.case == "gemm":
-        a, b = k.split_planes(rand(n, n)), k.split_planes(rand(n, n))
+        a, b = k.split_planes(rand(n, n), mixed=args.mixed), k.split_planes(rand(n, n), mixed=args.mixed)
         out = torch.zeros(n, n, device=device).T
         if args.mode == "store":
             fn = lambda: k.gemm(a, b, out=out)
         elif args.mode == "ema":
             fn = lambda: k.gemm(a, a, out=out, alpha=0.05, beta=0.95, symmetric=True)
         elif args.mode == "split":
-            planes = k.Planes.empty(n, n, device)
+            planes = k.Planes.empty(n, n, device, mixed=args.mixed)
             fn = lambda: k.gemm(a, b, mode=k.EPI_SPLIT, out_planes=planes)
         else:
-            planes = k.Planes.empty(n, n, device)
+            planes = k.Planes.empty(n, n, device, mixed=args.mixed)
             momentum, variance = torch.zeros(n, n, device=device).T, torch.zeros(n, n, device=device).T
             adam = dict(beta1=0.95, beta2=0.95, eps=1e-8, bias_correction1=0.5, bias_correction2=0.5)
             fn = lambda: k.gemm(a, b, mode=k.EPI_ADAM, out_planes=planes, momentum=momentum, variance=variance, adam=adam)
         us = timed(fn, args.repeats)
-        print(f"gemm_tf32x3 {args.mode} {n}^3: {us:.1f} us/launch, {2 * n**3 / us / 1e6:.1f} TFLOP/s fp32-equivalent "
-              f"({6 * n**3 / us / 1e6:.1f} TFLOP/s of tf32 MMA issued)")
+        form = "tf32 + 2 bf16 corrections" if args.mixed else "3 tf32 MMAs"
+        print(f"gemm_tf32x3 {args.mode} {n}^3 ({form}): {us:.1f} us/launch, {2 * n**3 / us / 1e6:.1f} TFLOP/s fp32-equivalent "
+              f"({(4 if args.mixed else 6) * n**3 / us / 1e6:.1f} TFLOP/s in tf32-MMA units)")
     elif args.case == "qr":
         matrix, Q = rand(n, n).T, torch.empty(n, n, device=device).T
         us = timed(lambda: qr.householder_qr(matrix.clone(), Q), args.repeats)

@@ -20,6 +20,7 @@
 //   barrier_kernel      one flag per peer in each rank's signal pad, release store to every peer,
 //                       bounded acquire spin on the own pad.  Used only when every rank has its own
 //                       GPU; ranks that share a GPU order themselves on the host instead.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
@@ -108,6 +109,20 @@ __device__ __forceinline__ float load_source(const DistSource& src, int gi, int 
   return __ldcg(source_address(src, gi, gj));  // bypass L1: peers rewrite these buffers between launches
 }
 
+// Where an output is written as operand planes: hi (fp32) and either lo (fp32) or the bf16 pair hb, lb.
+struct PlaneOut {
+  float* hi;
+  float* lo;          // null with hb: mixed planes; null without hb: plain copy into `hi`
+  uint16_t* hb;
+  uint16_t* lb;
+  int64_t d_j16;      // column pitch of the bf16 planes (elements)
+};
+
+__device__ __forceinline__ uint16_t bf16_bits_dev(float v) {
+  const __nv_bfloat16 b = __float2bfloat16_rn(v);
+  return *reinterpret_cast<const uint16_t*>(&b);
+}
+
 __device__ __forceinline__ float tf32_round_dev(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -119,7 +134,9 @@ __device__ __forceinline__ float tf32_round_dev(float x) {
 // read_i_fast tells whether consecutive i touch consecutive source addresses (chosen by the host).
 __global__ void __launch_bounds__(256)
 dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, int read_i_fast, int upper_only,
-                   float* out_hi, float* out_lo, int64_t d_i, int64_t d_j, int rows_out, int cols_out) {
+                   PlaneOut out, int64_t d_i, int64_t d_j, int rows_out, int cols_out) {
+  float* out_hi = out.hi;
+  float* out_lo = out.lo;
   __shared__ float tile[32][33];
   const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
   const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
@@ -139,7 +156,12 @@ dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose
     if (i < rows_out && j < cols_out && (!upper_only || map_index(map_i, i) < map_index(map_j, j))) {
       const float x = tile[t][tx];
       const int64_t off = i * d_i + j * d_j;
-      if (out_lo) {
+      if (out.hb) {
+        const float h = tf32_round_dev(x);
+        out_hi[off] = h;
+        out.hb[i * d_i + j * out.d_j16] = bf16_bits_dev(x);
+        out.lb[i * d_i + j * out.d_j16] = bf16_bits_dev(x - h);
+      } else if (out_lo) {
         const float h = tf32_round_dev(x);
         out_hi[off] = h;
         out_lo[off] = x - h;
@@ -168,7 +190,36 @@ __device__ __forceinline__ float4 load_group(const DistSource& src, bool transpo
   return v;
 }
 
-__device__ __forceinline__ void store_group(float* out_hi, float* out_lo, int64_t off, const float4& x, int limit) {
+__device__ __forceinline__ void store_group(const PlaneOut& out, int64_t i, int64_t j, int64_t d_j, const float4& x, int limit) {
+  float* out_hi = out.hi;
+  float* out_lo = out.lo;
+  const int64_t off = i + j * d_j;
+  if (out.hb) {
+    const int64_t off16 = i + j * out.d_j16;
+    const float v[4] = {x.x, x.y, x.z, x.w};
+    float h[4], l[4];
+    for (int e = 0; e < 4; ++e) {
+      h[e] = tf32_round_dev(v[e]);
+      l[e] = v[e] - h[e];
+    }
+    if (limit >= 4) {
+      *reinterpret_cast<float4*>(out_hi + off) = make_float4(h[0], h[1], h[2], h[3]);
+      const __nv_bfloat162 b0 = __floats2bfloat162_rn(v[0], v[1]), b1 = __floats2bfloat162_rn(v[2], v[3]);
+      const __nv_bfloat162 c0 = __floats2bfloat162_rn(l[0], l[1]), c1 = __floats2bfloat162_rn(l[2], l[3]);
+      uint2 pb, pc;
+      pb.x = *reinterpret_cast<const uint32_t*>(&b0); pb.y = *reinterpret_cast<const uint32_t*>(&b1);
+      pc.x = *reinterpret_cast<const uint32_t*>(&c0); pc.y = *reinterpret_cast<const uint32_t*>(&c1);
+      *reinterpret_cast<uint2*>(out.hb + off16) = pb;
+      *reinterpret_cast<uint2*>(out.lb + off16) = pc;
+    } else {
+      for (int e = 0; e < limit; ++e) {
+        out_hi[off + e] = h[e];
+        out.hb[off16 + e] = bf16_bits_dev(v[e]);
+        out.lb[off16 + e] = bf16_bits_dev(l[e]);
+      }
+    }
+    return;
+  }
   if (limit >= 4) {
     if (out_lo) {
       const float4 h = make_float4(tf32_round_dev(x.x), tf32_round_dev(x.y), tf32_round_dev(x.z), tf32_round_dev(x.w));
@@ -195,7 +246,7 @@ __device__ __forceinline__ void store_group(float* out_hi, float* out_lo, int64_
 // pass, four passes (four columns) in flight per thread; no shared memory.
 constexpr int kCopyTileI = 128, kCopyTileJ = 32;
 __global__ void __launch_bounds__(256)
-dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, float* out_hi, float* out_lo,
+dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, PlaneOut out,
                           int64_t d_j, int rows_out, int cols_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int i = blockIdx.x * kCopyTileI + 4 * lane;
@@ -212,7 +263,7 @@ dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
 #pragma unroll
   for (int pass = 0; pass < 4; ++pass) {
     const int j = j0 + 8 * pass;
-    if (j < cols_out) store_group(out_hi, out_lo, i + static_cast<int64_t>(j) * d_j, v[pass], limit);
+    if (j < cols_out) store_group(out, i, j, d_j, v[pass], limit);
   }
 }
 
@@ -220,7 +271,7 @@ dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
 // as 16-byte groups along i.
 constexpr int kTurnTile = 64;
 __global__ void __launch_bounds__(256)
-dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, float* out_hi, float* out_lo,
+dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, PlaneOut out,
                           int64_t d_j, int rows_out, int cols_out) {
   __shared__ float tile[kTurnTile][kTurnTile + 1];   // [i][j]
   const int i0 = blockIdx.x * kTurnTile, j0 = blockIdx.y * kTurnTile;
@@ -252,7 +303,7 @@ dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
     const int jl = line + 16 * pass, j = j0 + jl;
     if (j < cols_out) {
       const float4 x = make_float4(tile[4 * group][jl], tile[4 * group + 1][jl], tile[4 * group + 2][jl], tile[4 * group + 3][jl]);
-      store_group(out_hi, out_lo, i + static_cast<int64_t>(j) * d_j, x, limit);
+      store_group(out, i, j, d_j, x, limit);
     }
   }
 }
@@ -335,12 +386,14 @@ void register_comm(py::module_& m) {
     return py::bytes(reinterpret_cast<const char*>(prop.uuid.bytes), 16);
   });
 
-  m.def("dist_gather",
-        [](uint64_t peers, int kind, int rows, int cols, int nb_r, int nb_c, int Pr, int Pc, int world, int ip, int iP,
+  auto gather = [](uint64_t peers, int kind, int rows, int cols, int nb_r, int nb_c, int Pr, int Pc, int world, int ip, int iP,
            int inb, int ioff, uint64_t iperm, int jp, int jP, int jnb, int joff, uint64_t jperm, int transpose,
            int upper_only, int i_local_offset, int j_local_offset, uint64_t out_hi, uint64_t out_lo,
-           int64_t d_i, int64_t d_j, int rows_out, int cols_out, uint64_t stream) {
+           int64_t d_i, int64_t d_j, int rows_out, int cols_out, uint64_t stream, uint64_t out_hb, uint64_t out_lb,
+           int64_t d_j16) {
           if (rows_out <= 0 || cols_out <= 0) return;
+          PlaneOut out{reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), reinterpret_cast<uint16_t*>(out_hb),
+                       reinterpret_cast<uint16_t*>(out_lb), d_j16};
           DistSource src{reinterpret_cast<const float* const*>(peers), kind, rows, cols, nb_r, nb_c, Pr, Pc, world};
           IndexMap mi{ip, iP, inb, ioff, reinterpret_cast<const int64_t*>(iperm), i_local_offset};
           IndexMap mj{jp, jP, jnb, joff, reinterpret_cast<const int64_t*>(jperm), j_local_offset};
@@ -366,28 +419,37 @@ void register_comm(py::module_& m) {
           if (kind == kBlockCyclic) source_groups = (nb_r % 4 == 0);
           else if (kind == kRowShards) source_groups = (cols % 4 == 0);
           else source_groups = (world > 0 && (cols / world) % 4 == 0);
-          const bool aligned_out = d_i == 1 && d_j % 4 == 0 && (out_hi % 16 == 0) && (out_lo % 16 == 0);
+          const bool aligned_out = d_i == 1 && d_j % 4 == 0 && (out_hi % 16 == 0) && (out_lo % 16 == 0) &&
+                                   (out_hb == 0 || (d_j16 % 4 == 0 && out_hb % 8 == 0 && out_lb % 8 == 0));
           if (!upper_only && keeps_groups(along) && source_groups && aligned_out &&
               !g_force_scalar_gather) {
             if (read_i_fast) {
               dim3 grid((rows_out + kCopyTileI - 1) / kCopyTileI, (cols_out + kCopyTileJ - 1) / kCopyTileJ);
-              dist_gather_copy16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, reinterpret_cast<float*>(out_hi),
-                                                                      reinterpret_cast<float*>(out_lo), d_j, rows_out, cols_out);
+              dist_gather_copy16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, out, d_j, rows_out, cols_out);
               check(cudaGetLastError(), "dist_gather_copy16_kernel");
             } else {
               dim3 grid((rows_out + kTurnTile - 1) / kTurnTile, (cols_out + kTurnTile - 1) / kTurnTile);
-              dist_gather_turn16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, reinterpret_cast<float*>(out_hi),
-                                                                      reinterpret_cast<float*>(out_lo), d_j, rows_out, cols_out);
+              dist_gather_turn16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, out, d_j, rows_out, cols_out);
               check(cudaGetLastError(), "dist_gather_turn16_kernel");
             }
             return;
           }
           dim3 grid((rows_out + 31) / 32, (cols_out + 31) / 32);
           dist_gather_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-              src, mi, mj, transpose, read_i_fast, upper_only, reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), d_i,
-              d_j, rows_out, cols_out);
+              src, mi, mj, transpose, read_i_fast, upper_only, out, d_i, d_j, rows_out, cols_out);
           check(cudaGetLastError(), "dist_gather_kernel");
+        };
+  m.def("dist_gather",
+        [gather](uint64_t peers, int kind, int rows, int cols, int nb_r, int nb_c, int Pr, int Pc, int world, int ip, int iP,
+                 int inb, int ioff, uint64_t iperm, int jp, int jP, int jnb, int joff, uint64_t jperm, int transpose,
+                 int upper_only, int i_local_offset, int j_local_offset, uint64_t out_hi, uint64_t out_lo, int64_t d_i,
+                 int64_t d_j, int rows_out, int cols_out, uint64_t stream) {
+          gather(peers, kind, rows, cols, nb_r, nb_c, Pr, Pc, world, ip, iP, inb, ioff, iperm, jp, jP, jnb, joff, jperm,
+                 transpose, upper_only, i_local_offset, j_local_offset, out_hi, out_lo, d_i, d_j, rows_out, cols_out, stream,
+                 0, 0, 0);
         });
+  // the same with mixed operand planes as the output: hi (fp32) plus the bf16 planes hb, lb (column pitch d_j16)
+  m.def("dist_gather_mixed", gather);
 
   m.def("signal_flag", [](uint64_t flag, int value, uint64_t stream) {
     signal_flag_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int*>(flag), value);

@@ -3,6 +3,8 @@
 #include <stdexcept>
 #include <string>
 
+#include <cuda_bf16.h>
+
 #include "elementwise.h"
 
 namespace soapb200 {
@@ -67,9 +69,17 @@ __global__ void adam_flat4_kernel(const float4* __restrict__ g, float4* __restri
 // out(i, j) = src[i*s_i + j*s_j] for i < rows, j < cols, written as hi/lo planes with i contiguous
 // (pitch ldo).  A 32x33 shared tile makes both the read and the write coalesced whichever of s_i,
 // s_j is the unit stride, so the same kernel splits in place-order and transposes.
+__device__ __forceinline__ uint16_t bf16_bits(float v) {
+  const __nv_bfloat16 b = __float2bfloat16_rn(v);
+  return *reinterpret_cast<const uint16_t*>(&b);
+}
+
+// With `hb` / `lb` (bf16 planes, pitch ld16) the low part is written as bf16(x) and bf16(x - hi) instead of `lo`:
+// the operand format of the GEMM's mixed-precision corrections.
 __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restrict__ src, int64_t s_i, int64_t s_j,
                                                            float* __restrict__ hi, float* __restrict__ lo, int64_t ldo,
-                                                           int rows, int cols, float scale, int nearest) {
+                                                           int rows, int cols, float scale, int nearest,
+                                                           uint16_t* __restrict__ hb, uint16_t* __restrict__ lb, int64_t ld16) {
   __shared__ float tile[32][33];
   const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
   const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;  // 32 x 8
@@ -88,7 +98,12 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restri
       const float x = tile[t][tx] * scale;
       const float h = tf32_hi(x, nearest);
       hi[i + j * ldo] = h;
-      lo[i + j * ldo] = x - h;
+      if (hb != nullptr) {
+        hb[i + j * ld16] = bf16_bits(x);
+        lb[i + j * ld16] = bf16_bits(x - h);
+      } else {
+        lo[i + j * ldo] = x - h;
+      }
     }
   }
 }
@@ -155,10 +170,10 @@ void adam_update(const float* g, int64_t ldg, float* m, int64_t ldm, float* v, i
 }
 
 void split_planes(const float* src, int64_t s_i, int64_t s_j, float* hi, float* lo, int64_t ldo, int rows, int cols,
-                  float scale, int nearest, cudaStream_t stream) {
+                  float scale, int nearest, cudaStream_t stream, uint16_t* hb, uint16_t* lb, int64_t ld16) {
   if (rows <= 0 || cols <= 0) return;
   dim3 grid((rows + 31) / 32, (cols + 31) / 32);
-  split_planes_kernel<<<grid, 256, 0, stream>>>(src, s_i, s_j, hi, lo, ldo, rows, cols, scale, nearest);
+  split_planes_kernel<<<grid, 256, 0, stream>>>(src, s_i, s_j, hi, lo, ldo, rows, cols, scale, nearest, hb, lb, ld16);
   check_launch("split_planes_kernel");
 }
 

@@ -25,6 +25,15 @@ struct GemmOperands {
   // Extents of the whole operand buffers when a launch addresses sub-blocks of them per batch item
   // (0: the operand is exactly K x M, resp. K x N).
   int64_t a_k_total = 0, a_rows_total = 0, b_k_total = 0, b_rows_total = 0;
+  // Mixed-precision corrections (all four non-null selects them): bf16 planes hb ~ hi and lb ~ lo of each operand
+  // (pitches in bf16 elements, multiples of 8).  The two correction products hi*lo and lo*hi then run as
+  // kind::f16 MMAs at twice the tf32 rate; a_lo and b_lo are not read.
+  const uint16_t* a_hb = nullptr;
+  const uint16_t* a_lb = nullptr;
+  int64_t lda16 = 0;
+  const uint16_t* b_hb = nullptr;
+  const uint16_t* b_lb = nullptr;
+  int64_t ldb16 = 0;
 };
 
 struct GemmProblem {
@@ -43,6 +52,9 @@ struct GemmProblem {
   float* Chi;
   float* Clo;
   int64_t ldp;
+  uint16_t* Chb;     // kEpiSplit / kEpiAdam with mixed output planes: bf16(value) and bf16(value - hi) instead of Clo
+  uint16_t* Clb;
+  int64_t ldp16;
   float* mom;
   float* var;
   int64_t ldm, ldv;

@@ -20,6 +20,7 @@
 // Replaces the SLATE gemm calls of the reference (src/soap_tp/csrc/slate_bindings.cpp:55-123 and
 // :191-277), which run batched cuBLAS SGEMM on 128^3 tiles with MPI tile broadcasts in between.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -72,8 +73,23 @@ struct TileConfig {
 };
 
 struct alignas(64) GemmMaps {
-  CUtensorMap a_hi, a_lo, b_hi, b_lo;
+  CUtensorMap a_hi, a_lo, b_hi, b_lo;     // MIXED: a_lo / b_lo describe the bf16 plane hb
+  CUtensorMap a_lb, b_lb;                 // MIXED only: the bf16 plane lb
 };
+
+// Four consecutive rows of one column as bf16 (8 bytes).
+__device__ __forceinline__ void store4_bf16(uint16_t* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+  const __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = packed;
+}
+__device__ __forceinline__ uint16_t bf16_bits(float v) {
+  const __nv_bfloat16 b = __float2bfloat16_rn(v);
+  return *reinterpret_cast<const uint16_t*>(&b);
+}
 
 __device__ __forceinline__ float tf32_round(float x) {
   uint32_t r;
@@ -124,7 +140,13 @@ __device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t
     if (prob.beta != 0.0f) v = fmaf(prob.beta, prob.Chi[off] + prob.Clo[off], v);  // planes hold the old value
     const float hi = tf32_round(v);
     prob.Chi[off] = hi;
-    prob.Clo[off] = v - hi;
+    if (prob.Chb) {
+      const int64_t off16 = m + static_cast<int64_t>(n) * prob.ldp16;
+      prob.Chb[off16] = bf16_bits(v);
+      prob.Clb[off16] = bf16_bits(v - hi);
+    } else {
+      prob.Clo[off] = v - hi;
+    }
     if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = v;
   } else if constexpr (MODE == kEpiAdam) {
     float* mp = prob.mom + m + static_cast<int64_t>(n) * prob.ldm;
@@ -138,7 +160,13 @@ __device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t
       const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
       const float hi = tf32_round(u);
       prob.Chi[off] = hi;
-      prob.Clo[off] = u - hi;
+      if (prob.Chb) {
+        const int64_t off16 = m + static_cast<int64_t>(n) * prob.ldp16;
+        prob.Chb[off16] = bf16_bits(u);
+        prob.Clb[off16] = bf16_bits(u - hi);
+      } else {
+        prob.Clo[off] = u - hi;
+      }
     }
     if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = u;
   }
@@ -188,7 +216,12 @@ __device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t
       lo.v[i] = v - hi.v[i];
     }
     store4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp, hi);
-    store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
+    if (prob.Chb) {
+      store4_bf16(prob.Chb + m + static_cast<int64_t>(n) * prob.ldp16, plain.v);
+      store4_bf16(prob.Clb + m + static_cast<int64_t>(n) * prob.ldp16, lo.v);
+    } else {
+      store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
+    }
     if (prob.C) store4(prob.C + m + static_cast<int64_t>(n) * prob.ldc, plain);
   } else if constexpr (MODE == kEpiAdam) {
     Vec4 mo, va, u, hi, lo;
@@ -205,7 +238,12 @@ __device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t
     store4(prob.var + m + static_cast<int64_t>(n) * prob.ldv, va);
     if (prob.Chi) {
       store4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp, hi);
-      store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
+      if (prob.Chb) {
+        store4_bf16(prob.Chb + m + static_cast<int64_t>(n) * prob.ldp16, u.v);
+        store4_bf16(prob.Clb + m + static_cast<int64_t>(n) * prob.ldp16, lo.v);
+      } else {
+        store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
+      }
     }
     if (prob.C) store4(prob.C + m + static_cast<int64_t>(n) * prob.ldc, u);
   }
@@ -232,6 +270,8 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
   }
   bool vector = rows == kBM && !(prob.symmetric == 2 && ((prob.tri_nb | prob.tri_m0) & 3) != 0);
   if constexpr (MODE == kEpiStore) vector = vector && aligned16(prob.C + c_shift, prob.ldc);
+  if (prob.Chb != nullptr)
+    vector = vector && (prob.ldp16 & 3) == 0 && ((reinterpret_cast<uintptr_t>(prob.Chb) | reinterpret_cast<uintptr_t>(prob.Clb)) & 7) == 0;
   if constexpr (MODE == kEpiSplit)
     vector = vector && aligned16(prob.Chi, prob.ldp) && aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);
   if constexpr (MODE == kEpiAdam)
@@ -320,9 +360,10 @@ __device__ __forceinline__ void run_pair_update(const GemmProblem& prob, const f
   }
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool MIXED>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmProblem prob, int* status) {
+  // (the mixed variant needs the 32-element k-block build: 128-byte fp32 rows and 64-byte bf16 rows; the host refuses otherwise)
   using Cfg = TileConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -370,6 +411,10 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
     tma_prefetch_descriptor(&maps.a_lo);
     tma_prefetch_descriptor(&maps.b_hi);
     tma_prefetch_descriptor(&maps.b_lo);
+    if constexpr (MIXED) {
+      tma_prefetch_descriptor(&maps.a_lb);
+      tma_prefetch_descriptor(&maps.b_lb);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -402,10 +447,21 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
       const int batch = blockIdx.z;
       const int ka = k0 + batch * prob.a_k_step, kbb = k0 + batch * prob.b_k_step;
       const int ra = m0 + batch * prob.a_row_step, rb = n0 + batch * prob.b_row_step;
-      tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
-      tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka, ra);
-      tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], kbb, rb);
-      tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb, rb);
+      if constexpr (MIXED) {
+        // per operand: hi as fp32 (128-byte rows), then hb and lb as bf16 (64-byte rows): the same bytes as hi + lo
+        tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
+        tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka, ra);
+        tma_load_2d(stage + kBM * kRowBytes + kBM * (kRowBytes / 2), &maps.a_lb, &full_bar[s], ka, ra);
+        uint8_t* b_stage = stage + 2 * kBM * kRowBytes;
+        tma_load_2d(b_stage, &maps.b_hi, &full_bar[s], kbb, rb);
+        tma_load_2d(b_stage + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb, rb);
+        tma_load_2d(b_stage + BN * kRowBytes + BN * (kRowBytes / 2), &maps.b_lb, &full_bar[s], kbb, rb);
+      } else {
+        tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
+        tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka, ra);
+        tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], kbb, rb);
+        tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb, rb);
+      }
     }
     if (*abort_flag) {
       // give copies that are still in flight time to land before the CTA's shared memory is released
@@ -432,6 +488,32 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t stage = smem_u32(smem + s * Cfg::kStageBytes);
+        if constexpr (MIXED) {
+          constexpr uint32_t idesc16 = umma_idesc_bf16(kBM, BN);
+          constexpr int kHalf = kRowBytes / 2;
+          const uint32_t b_stage = stage + 2 * kBM * kRowBytes;
+          const uint64_t a_hi = umma_desc_kmajor<kRowBytes>(stage);
+          const uint64_t a_hb = umma_desc_kmajor<kHalf>(stage + kBM * kRowBytes);
+          const uint64_t a_lb = umma_desc_kmajor<kHalf>(stage + kBM * kRowBytes + kBM * kHalf);
+          const uint64_t b_hi = umma_desc_kmajor<kRowBytes>(b_stage);
+          const uint64_t b_hb = umma_desc_kmajor<kHalf>(b_stage + BN * kRowBytes);
+          const uint64_t b_lb = umma_desc_kmajor<kHalf>(b_stage + BN * kRowBytes + BN * kHalf);
+          // the two correction products as bf16 MMAs (16 elements of K = 32 bytes each), then hi*hi in tf32
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+            umma_bf16_ss(tmem_acc, a_lb + adv, b_hb + adv, idesc16, first ? 0u : 1u);
+            first = 0;
+            umma_bf16_ss(tmem_acc, a_hb + adv, b_lb + adv, idesc16, 1);
+          }
+#pragma unroll
+          for (int k = 0; k < kBK / 8; ++k) {
+            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+            umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+          }
+          umma_commit(&empty_bar[s]);
+          continue;
+        }
         const uint64_t a_hi = umma_desc_kmajor<kRowBytes>(stage);
         const uint64_t a_lo = umma_desc_kmajor<kRowBytes>(stage + kBM * kRowBytes);
         const uint64_t b_hi = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes);
@@ -549,23 +631,48 @@ CUtensorMap make_operand_map(const float* base, int64_t K, int64_t rows, int64_t
   return map;
 }
 
-template <int BN, int MODE>
+// K-contiguous bf16 matrix [rows][K] with row pitch ld (elements); box = 32 elements (64 bytes) x box_rows rows.
+CUtensorMap make_bf16_map(const uint16_t* base, int64_t K, int64_t rows, int64_t ld, int box_rows) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) throw std::invalid_argument("bf16 operand plane must be 16-byte aligned");
+  if ((ld * 2) % 16 != 0) throw std::invalid_argument("bf16 operand plane pitch must be a multiple of 8 elements");
+  CUtensorMap map;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(base), dims, strides, box,
+                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled (bf16) failed with code " + std::to_string(res));
+  return map;
+}
+
+template <int BN, int MODE, bool MIXED>
 void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
   using Cfg = TileConfig<BN>;
   static PerDeviceOnce configured;
-  allow_dynamic_smem(reinterpret_cast<const void*>(gemm_tf32x3_kernel<BN, MODE>), Cfg::kSmemBytes, configured, "gemm_tf32x3");
+  allow_dynamic_smem(reinterpret_cast<const void*>(gemm_tf32x3_kernel<BN, MODE, MIXED>), Cfg::kSmemBytes, configured, "gemm_tf32x3");
   GemmMaps maps;
   const int64_t a_k = ops.a_k_total ? ops.a_k_total : prob.K, a_rows = ops.a_rows_total ? ops.a_rows_total : prob.M;
   const int64_t b_k = ops.b_k_total ? ops.b_k_total : prob.K, b_rows = ops.b_rows_total ? ops.b_rows_total : prob.N;
   maps.a_hi = make_operand_map(ops.a_hi, a_k, a_rows, ops.lda, kBM);
-  maps.a_lo = make_operand_map(ops.a_lo, a_k, a_rows, ops.lda, kBM);
   maps.b_hi = make_operand_map(ops.b_hi, b_k, b_rows, ops.ldb, BN);
-  maps.b_lo = make_operand_map(ops.b_lo, b_k, b_rows, ops.ldb, BN);
+  if constexpr (MIXED) {
+    maps.a_lo = make_bf16_map(ops.a_hb, a_k, a_rows, ops.lda16, kBM);
+    maps.a_lb = make_bf16_map(ops.a_lb, a_k, a_rows, ops.lda16, kBM);
+    maps.b_lo = make_bf16_map(ops.b_hb, b_k, b_rows, ops.ldb16, BN);
+    maps.b_lb = make_bf16_map(ops.b_lb, b_k, b_rows, ops.ldb16, BN);
+  } else {
+    maps.a_lo = make_operand_map(ops.a_lo, a_k, a_rows, ops.lda, kBM);
+    maps.b_lo = make_operand_map(ops.b_lo, b_k, b_rows, ops.ldb, BN);
+    maps.a_lb = maps.a_lo;
+    maps.b_lb = maps.b_lo;
+  }
   const int tiles_m = (prob.M + kBM - 1) / kBM;
   const int tiles_n = (prob.N + BN - 1) / BN;
   const int splits = (MODE == kEpiStore && prob.k_splits > 1) ? prob.k_splits : 1;
   dim3 grid(tiles_m * tiles_n, splits, prob.batches > 1 ? prob.batches : 1);
-  gemm_tf32x3_kernel<BN, MODE><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(maps, prob, status);
+  gemm_tf32x3_kernel<BN, MODE, MIXED><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(maps, prob, status);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) throw std::runtime_error(std::string("gemm_tf32x3 launch: ") + cudaGetErrorString(err));
 }
@@ -578,27 +685,39 @@ void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, 
   // Wide tiles when there are enough of them to fill the 148 SMs; narrower tiles otherwise.
   const int64_t wide_tiles = static_cast<int64_t>((prob.M + kBM - 1) / kBM) * ((prob.N + 255) / 256);
   const bool wide = prob.N > 128 && wide_tiles >= 148 && !prob.force_narrow;
+  const bool mixed = ops.a_hb && ops.a_lb && ops.b_hb && ops.b_lb;
+  if (mixed && kBK != 32) throw std::invalid_argument("gemm_tf32x3: mixed corrections need the 32-element k-block build");
+#define SOAP_GEMM_LAUNCH(MODE_)                                                                      \
+  do {                                                                                               \
+    if (mixed) {                                                                                     \
+      wide ? launch<256, MODE_, true>(ops, prob, status, stream) : launch<128, MODE_, true>(ops, prob, status, stream);   \
+    } else {                                                                                         \
+      wide ? launch<256, MODE_, false>(ops, prob, status, stream) : launch<128, MODE_, false>(ops, prob, status, stream); \
+    }                                                                                                \
+  } while (0)
   switch (prob.mode) {
     case kEpiStore:
-      wide ? launch<256, kEpiStore>(ops, prob, status, stream) : launch<128, kEpiStore>(ops, prob, status, stream);
+      SOAP_GEMM_LAUNCH(kEpiStore);
       break;
     case kEpiSplit:
-      wide ? launch<256, kEpiSplit>(ops, prob, status, stream) : launch<128, kEpiSplit>(ops, prob, status, stream);
+      SOAP_GEMM_LAUNCH(kEpiSplit);
       break;
     case kEpiAdam:
-      wide ? launch<256, kEpiAdam>(ops, prob, status, stream) : launch<128, kEpiAdam>(ops, prob, status, stream);
+      SOAP_GEMM_LAUNCH(kEpiAdam);
       break;
     case kEpiRowMajor:
-      wide ? launch<256, kEpiRowMajor>(ops, prob, status, stream) : launch<128, kEpiRowMajor>(ops, prob, status, stream);
+      SOAP_GEMM_LAUNCH(kEpiRowMajor);
       break;
     case kEpiPairUpdate:
       if (prob.N != 128 || prob.remap == nullptr || prob.Chi == nullptr)
         throw std::invalid_argument("gemm_tf32x3: the pair update needs N = 128, a remap table and output planes");
-      launch<128, kEpiPairUpdate>(ops, prob, status, stream);
+      if (mixed) throw std::invalid_argument("gemm_tf32x3: the pair update takes fp32 planes only");
+      launch<128, kEpiPairUpdate, false>(ops, prob, status, stream);
       break;
     default:
       throw std::invalid_argument("gemm_tf32x3: unknown epilogue mode");
   }
+#undef SOAP_GEMM_LAUNCH
 }
 
 }  // namespace soapb200

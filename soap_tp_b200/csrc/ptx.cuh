@@ -96,6 +96,16 @@ __device__ __forceinline__ void umma_tf32_ss(uint32_t tmem_d, uint64_t desc_a, u
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with bf16 inputs (kind::f16), K = 16 per instruction.
+__device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on an mbarrier once all previously issued UMMAs of this thread have completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -124,17 +134,23 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // SWIZZLE_64B (4).
 template <int RowBytes>
 __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t smem_addr) {
-  static_assert(RowBytes == 128 || RowBytes == 64, "one swizzle row per k-block");
+  static_assert(RowBytes == 128 || RowBytes == 64 || RowBytes == 32, "one swizzle row per k-block");
   uint64_t desc = static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   desc |= static_cast<uint64_t>(1) << 16;
   desc |= static_cast<uint64_t>((8 * RowBytes) >> 4) << 32;
   desc |= static_cast<uint64_t>(1) << 46;
-  desc |= static_cast<uint64_t>(RowBytes == 128 ? 2 : 4) << 61;
+  desc |= static_cast<uint64_t>(RowBytes == 128 ? 2 : (RowBytes == 64 ? 4 : 6)) << 61;   // SWIZZLE_128B / 64B / 32B
   return desc;
 }
 // kind::tf32, fp32 accumulator, both operands K-major, no negation, dense.
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// kind::f16 with bf16 inputs, fp32 accumulator, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 

@@ -9,7 +9,7 @@
 //                        Per column: the Householder vector v of the updated column, y = A v by streaming the
 //                        trailing matrix once (every warp owns columns; A is kept with both triangles, so a
 //                        column IS a row and all loads are contiguous), and w = tau (y - tau/2 (y.v) v) with
-//                        the pending rank-2 updates of the panel applied implicitly.  Three grid barriers per
+//                        the pending rank-2 updates of the panel applied implicitly.  Two grid barriers per
 //                        column.  The deferred update A -= V W^T + W V^T is one tensor-core GEMM per panel
 //                        (K = 64), for which the kernel leaves [V|W] and [W|V] as operand planes; it also
 //                        leaves V, V^T and the compact-WY factor T in the formats of the QR panel kernel so
@@ -131,28 +131,15 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
     for (int idx = t; idx < kTB * (kTB + 1); idx += kThreads) (&T[0][0])[idx] = 0.f;
     if (t < kTB) taus[t] = 0.f;
   }
-  // rows of the [V | W] store start out as zeros for this panel
+  // rows of the [V | W] store start out as zeros for this panel (every thread clears the rows it owns)
   for (int i = gid; i < n; i += row_stride)
     for (int c = 0; c < kRowPitch; ++c) a.vw[static_cast<int64_t>(i) * kRowPitch + c] = 0.f;
-  if (!grid_barrier(a.barrier, target, a.status)) return;
+  if (t < kRowPitch) rowj[t] = 0.f;
+  __syncthreads();
 
-  // the previous column's scalars, from which row j of W follows without waiting for its owner's store
-  float tau_prev = 0.f, coef_prev = 0.f;
-  bool alive = true;
-
-  for (int k = 0; k < a.nb && alive; ++k) {
-    const int j = a.j0 + k;                      // column being reduced; its vector lives in rows j+1 .. n-1
-    // ---- phase 0: the updated column a = A[:, j] - V W[j, :]^T - W V[j, :]^T, its norm, the diagonal entry ----
-    // row j of V and W: entries of columns < k-1 are in the store; column k-1 is rebuilt from y[j] (see above)
-    if (t < kRowPitch) {
-      const int c = t % kTB;
-      const bool w_part = t >= kTB;
-      float value = 0.f;
-      if (c < k - 1) value = __ldcg(&a.vw[static_cast<int64_t>(j) * kRowPitch + t]);
-      else if (c == k - 1) value = w_part ? fmaf(tau_prev, __ldcg(&a.y[j]), coef_prev) : 1.f;   // v_{k-1} starts with 1 in row j
-      rowj[t] = value;
-    }
-    __syncthreads();
+  // Column update of column `j` (k-th of the panel) for the rows this thread owns, from the panel's reflectors so
+  // far (`rowj` holds row j of [V | W]): writes x, the diagonal entry and this CTA's part of |x[j+2:]|^2.
+  auto column_update = [&](int j, int k) {
     float sumsq = 0.f;
     for (int i = gid; i < n; i += row_stride) {
       if (i < j) continue;
@@ -168,9 +155,14 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
     }
     const float cta_sumsq = block_sum(sumsq, scratch);
     if (t == 0) partial[0] = cta_sumsq;
-    if (!grid_barrier(a.barrier, target, a.status)) { alive = false; break; }
+  };
 
-    // ---- phase 1: Householder scalars (every thread), v into shared memory, y = A v, partial p and q ----
+  column_update(a.j0, 0);
+  bool alive = grid_barrier(a.barrier, target, a.status);
+
+  for (int k = 0; k < a.nb && alive; ++k) {
+    const int j = a.j0 + k;                      // column being reduced; its vector lives in rows j+1 .. n-1
+    // ---- phase B: Householder scalars (every thread), v into shared memory, y = A v, partial p, q and y.v ----
     const float sigma = sum_over_ctas(a.partial, 0, G, &bcast);
     const float alpha = __ldcg(&a.x[j + 1]);
     float tau = 0.f, scale = 0.f, beta = alpha;
@@ -185,48 +177,47 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
       else if (i > j + 1) value = __ldcg(&a.x[i]) * scale;
       v_s[i] = value;
     }
-    if (t < kRowPitch) {
-      for (int w = 0; w < kWarps; ++w) red_w[w][t] = 0.f;
-    }
     __syncthreads();
-    // rows: store v in the V part, accumulate p_c = sum_i W[i][c] v_i and q_c = sum_i V[i][c] v_i (c < k)
+    // q_c = sum_i V[i][c] v_i and p_c = sum_i W[i][c] v_i over this CTA's rows: thread (value, group) walks every
+    // eighth row of the slab, so the loads of a warp are contiguous and nothing is shuffled
     {
-      for (int c = 0; c < k; ++c) {
-        float q_part = 0.f, p_part = 0.f;
-        for (int i = gid; i < n; i += row_stride) {
-          if (i <= j) continue;
-          const float vi = v_s[i];
-          const float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
-          q_part = fmaf(mine[c], vi, q_part);
-          p_part = fmaf(mine[kTB + c], vi, p_part);
-        }
-        q_part = warp_sum(q_part);
-        p_part = warp_sum(p_part);
-        if (lane == 0) {
-          red_w[warp][c] = q_part;
-          red_w[warp][kTB + c] = p_part;
-        }
+      const int value = t % kRowPitch, group = t / kRowPitch;
+      float acc = 0.f;
+      if (value % kTB < k) {
+        for (int base = blockIdx.x * kThreads; base < n; base += row_stride)
+          for (int r = group; r < kThreads; r += kThreads / kRowPitch) {
+            const int i = base + r;
+            if (i > j && i < n) acc = fmaf(__ldcg(&a.vw[static_cast<int64_t>(i) * kRowPitch + value]), v_s[i], acc);
+          }
       }
-      for (int i = gid; i < n; i += row_stride)
-        if (i > j) a.vw[static_cast<int64_t>(i) * kRowPitch + k] = v_s[i];
+      red_w[group][value] = acc;
     }
-    // y = A[j+1:, j+1:] v: warp per column, lanes along the (contiguous) rows
+    for (int i = gid; i < n; i += row_stride)
+      if (i > j) a.vw[static_cast<int64_t>(i) * kRowPitch + k] = v_s[i];
+    // y = A[j+1:, j+1:] v: warp per column, lanes along the (contiguous) rows; y.v on the way
+    float yv = 0.f;
     {
       const int first = j + 1;
       const int l0 = first & ~3;
       const int n4 = n & ~3;
       for (int c = first + gwarp; c < n; c += total_warps) {
         const float* col = a.A + static_cast<int64_t>(c) * lda;
-        float acc0 = 0.f, acc1 = 0.f;
+        float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
         if (vec_ok) {
           int l = l0 + 4 * lane;
-          for (; l + 128 < n4; l += 256) {
+          for (; l + 384 < n4; l += 512) {
             const float4 m0 = __ldg(reinterpret_cast<const float4*>(col + l));
             const float4 m1 = __ldg(reinterpret_cast<const float4*>(col + l + 128));
+            const float4 m2 = __ldg(reinterpret_cast<const float4*>(col + l + 256));
+            const float4 m3 = __ldg(reinterpret_cast<const float4*>(col + l + 384));
             const float4 x0 = *reinterpret_cast<const float4*>(&v_s[l]);
             const float4 x1 = *reinterpret_cast<const float4*>(&v_s[l + 128]);
+            const float4 x2 = *reinterpret_cast<const float4*>(&v_s[l + 256]);
+            const float4 x3 = *reinterpret_cast<const float4*>(&v_s[l + 384]);
             acc0 = fmaf(m0.x, x0.x, acc0); acc0 = fmaf(m0.y, x0.y, acc0); acc0 = fmaf(m0.z, x0.z, acc0); acc0 = fmaf(m0.w, x0.w, acc0);
             acc1 = fmaf(m1.x, x1.x, acc1); acc1 = fmaf(m1.y, x1.y, acc1); acc1 = fmaf(m1.z, x1.z, acc1); acc1 = fmaf(m1.w, x1.w, acc1);
+            acc2 = fmaf(m2.x, x2.x, acc2); acc2 = fmaf(m2.y, x2.y, acc2); acc2 = fmaf(m2.z, x2.z, acc2); acc2 = fmaf(m2.w, x2.w, acc2);
+            acc3 = fmaf(m3.x, x3.x, acc3); acc3 = fmaf(m3.y, x3.y, acc3); acc3 = fmaf(m3.z, x3.z, acc3); acc3 = fmaf(m3.w, x3.w, acc3);
           }
           for (; l < n4; l += 128) {
             const float4 m0 = __ldg(reinterpret_cast<const float4*>(col + l));
@@ -237,22 +228,25 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
         } else {
           for (int l = first + lane; l < n; l += 32) acc0 = fmaf(__ldg(col + l), v_s[l], acc0);
         }
-        const float total = warp_sum(acc0 + acc1);
-        if (lane == 0) a.y[c] = total;
+        const float total = warp_sum((acc0 + acc1) + (acc2 + acc3));
+        if (lane == 0) {
+          a.y[c] = total;
+          yv = fmaf(total, v_s[c], yv);
+        }
       }
     }
-    __syncthreads();
+    const float cta_yv = block_sum(yv, scratch);       // (its barriers also order red_w)
     if (t < kRowPitch) {
       float total = 0.f;
-      for (int w = 0; w < kWarps; ++w) total += red_w[w][t];
+      for (int g = 0; g < kThreads / kRowPitch; ++g) total += red_w[g][t];
       partial[1 + t] = total;
     }
+    if (t == 0) partial[kRowPitch + 1] = cta_yv;
     if (!grid_barrier(a.barrier, target, a.status)) { alive = false; break; }
 
-    // ---- phase 2: p and q over all CTAs, corrected y, partial y.v; CTA 0: column k of T ----
+    // ---- phase C: p, q and s = y'.v over all CTAs; w for the own rows; then the update of the next column ----
     {
-      // 64 values x 8 interleaved segments of the CTAs, then the segments in index order
-      const int value = t % kRowPitch, segment = t / kRowPitch;       // 512 threads = 64 x 8
+      const int value = t % kRowPitch, segment = t / kRowPitch;       // 512 threads = 64 values x 8 segments of CTAs
       float total = 0.f;
       for (int g = segment; g < G; g += kThreads / kRowPitch)
         total += __ldcg(&a.partial[static_cast<int64_t>(g) * kPartialPitch + 1 + value]);
@@ -264,15 +258,18 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
         pq[t] = sum;                               // q in [0, kTB), p in [kTB, 2 kTB)
       }
     }
-    __syncthreads();
-    float yv = 0.f;
+    const float yv_raw = sum_over_ctas(a.partial, kRowPitch + 1, G, &bcast);    // (syncs: pq is visible after it)
+    // y' = y - V p - W q, hence y'.v = y.v - q.p - p.q
+    float qp = 0.f;
+    for (int c = 0; c < k; ++c) qp = fmaf(pq[c], pq[kTB + c], qp);
+    const float s = yv_raw - 2.f * qp;
+    const float coef = -0.5f * tau * tau * s;
     for (int i = gid; i < n; i += row_stride) {
       if (i <= j) continue;
       float value = __ldcg(&a.y[i]);
-      const float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
+      float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
       for (int c = 0; c < k; ++c) value -= mine[c] * pq[kTB + c] + mine[kTB + c] * pq[c];
-      a.y[i] = value;
-      yv = fmaf(value, v_s[i], yv);
+      mine[kTB + k] = fmaf(tau, value, coef * v_s[i]);          // w = tau y' - (tau^2 / 2) (y'.v) v
     }
     if (blockIdx.x == 0) {
       // T[0:k, k] = -tau T[0:k, 0:k] q[0:k], T[k][k] = tau
@@ -288,22 +285,28 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
         a.e[j] = static_cast<double>(beta);
       }
     }
-    const float cta_yv = block_sum(yv, scratch);
-    if (t == 0) partial[kRowPitch + 1] = cta_yv;
+    if (k + 1 < a.nb) {
+      // row j+1 of [V | W] for the next column: stored entries for the older reflectors, rebuilt ones for this one
+      // (v starts with 1 in row j+1; its w entry follows from y[j+1], p, q, which every CTA has)
+      const int jn = j + 1;
+      __syncthreads();                            // rowj is still read by nobody; pq is complete
+      if (t < kRowPitch) {
+        const int c = t % kTB;
+        rowj[t] = (c < k) ? __ldcg(&a.vw[static_cast<int64_t>(jn) * kRowPitch + t]) : 0.f;
+      }
+      __syncthreads();
+      if (t == 0) {
+        float value = __ldcg(&a.y[jn]);
+        for (int c = 0; c < k; ++c) value -= rowj[c] * pq[kTB + c] + rowj[kTB + c] * pq[c];
+        rowj[k] = 1.f;
+        rowj[kTB + k] = fmaf(tau, value, coef);
+      }
+      __syncthreads();
+      column_update(jn, k + 1);
+    }
     if (!grid_barrier(a.barrier, target, a.status)) { alive = false; break; }
-
-    // ---- phase 3: w = tau y - (tau^2 / 2) (y.v) v into the W part (own rows) ----
-    const float s = sum_over_ctas(a.partial, kRowPitch + 1, G, &bcast);
-    const float coef = -0.5f * tau * tau * s;
-    for (int i = gid; i < n; i += row_stride)
-      if (i > j) a.vw[static_cast<int64_t>(i) * kRowPitch + kTB + k] = fmaf(tau, __ldcg(&a.y[i]), coef * v_s[i]);
-    tau_prev = tau;
-    coef_prev = coef;      // times v[j+1] = 1 for the row the next column needs
-    __syncthreads();
   }
-  if (!alive) return;
-  // every row's W entry of the last column must be visible before the store is read across CTAs
-  if (!grid_barrier(a.barrier, target, a.status)) return;
+  if (!alive) return;      // (the loop's last barrier made every row of the store visible to all CTAs)
 
   const int next = a.j0 + a.nb;                    // first row / column of the trailing matrix
   // ---- outputs ----

@@ -75,19 +75,24 @@ def dist_gather(src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, co
     """``out(i, j) = src(map_i(i), map_j(j))`` (``src(map_j(j), map_i(i))`` if ``transpose``)."""
     if rows_out <= 0 or cols_out <= 0:
         return
+    extra = ()
     if planes is not None:
-        hi, lo, d_i, d_j = planes.hi.data_ptr(), planes.lo.data_ptr(), 1, planes.ld
+        low = planes.low_pointers()
+        hi, lo, d_i, d_j = planes.hi.data_ptr(), low["lo"], 1, planes.ld
+        if planes.mixed:
+            extra = (low["hb"], low["lb"], low["ld16"])
     else:
         assert out is not None
         hi, lo = out.data_ptr(), 0
         d_i = out.stride(0) if out.shape[0] > 1 else 1
         d_j = out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0])
-    k._C.dist_gather(
+    launch = k._C.dist_gather_mixed if extra else k._C.dist_gather
+    launch(
         src.segment.peer_table.data_ptr(), src.kind, src.rows, src.cols, src.nb_r, src.nb_c, src.Pr, src.Pc, src.world,
         map_i.p, map_i.P, map_i.nb, map_i.offset, map_i.perm.data_ptr() if map_i.perm is not None else 0,
         map_j.p, map_j.P, map_j.nb, map_j.offset, map_j.perm.data_ptr() if map_j.perm is not None else 0,
         int(transpose), int(upper_only), map_i.local_offset, map_j.local_offset, hi, lo, d_i, d_j, rows_out, cols_out,
-        k._stream())
+        k._stream(), *extra)
     k._count("dist_gather_kernel")
     if out is not None:
         k.mark_written(out)
@@ -128,11 +133,14 @@ class GridEngine:
     def col_map(self, perm: Optional[Tensor] = None) -> IndexMap:
         return IndexMap(self.pc, self.Pc, self.nb, 0, perm)
 
-    def planes(self, tag: str, depth: int, cols: int) -> k.Planes:
-        key = (tag, depth, cols)
+    def planes(self, tag: str, depth: int, cols: int, classic: bool = False) -> k.Planes:
+        """Cached operand planes.  The operands of the optimizer-step products are mixed planes (``kernels.Planes``);
+        ``classic`` asks for fp32 hi/lo planes (operands of the power iteration, which feeds the QR)."""
+        mixed = k.MIXED_CORRECTIONS and not classic
+        key = (tag, depth, cols, mixed)
         found = self._planes.get(key)
         if found is None:
-            found = k.Planes.empty(depth, cols, self.device)
+            found = k.Planes.empty(depth, cols, self.device, mixed=mixed)
             self._planes[key] = found
         return found
 
@@ -186,8 +194,8 @@ class GridEngine:
         source = self.stage_packed("basis", Q, (size, size))
         self.comm.barrier()
         cols = self.cols_of(size)
-        plain = entry.get("plain") or k.Planes.empty(size, cols, self.device)
-        transposed = entry.get("transposed") or k.Planes.empty(size, cols, self.device)
+        plain = entry.get("plain") or k.Planes.empty(size, cols, self.device, mixed=k.MIXED_CORRECTIONS)
+        transposed = entry.get("transposed") or k.Planes.empty(size, cols, self.device, mixed=k.MIXED_CORRECTIONS)
         dist_gather(source, IDENTITY, self.col_map(), size, cols, planes=plain)
         dist_gather(source, IDENTITY, self.col_map(), size, cols, transpose=True, planes=transposed)
         self.comm.barrier()
@@ -511,7 +519,7 @@ def _product_with_basis(e: GridEngine, P: Tensor, Q: Tensor, work: Tensor, size:
     q_source = e.stage_packed("basis", Q, (size, size))
     e.comm.barrier()
     lr, lc = e.rows_of(size), e.cols_of(size)
-    a, b = e.planes("panel_a", size, lr), e.planes("panel_b", size, lc)
+    a, b = e.planes("power_a", size, lr, classic=True), e.planes("power_b", size, lc, classic=True)
     dist_gather(p_source, IDENTITY, e.row_map(), size, lr, planes=a)
     dist_gather(q_source, IDENTITY, e.col_map(), size, lc, planes=b)
     k.gemm(a, b, out=work[: max(1, lr), : max(1, lc)])

@@ -146,38 +146,73 @@ def round_up(value: int, multiple: int) -> int:
     return -(-value // multiple) * multiple
 
 
+# SOAP_TP_MIXED_CORRECTIONS=0 keeps every product on three tf32 MMAs per k-step.  By default the products of the
+# optimizer step (rotations, Gram EMAs, momentum transport) take their two correction terms as bf16 MMAs, see
+# ``Planes``; the factorisations (QR, eigensolvers, power iteration) always use the full 3xTF32 form.
+MIXED_CORRECTIONS = os.environ.get("SOAP_TP_MIXED_CORRECTIONS", "1") != "0"
+
+
 @dataclass
 class Planes:
-    """hi/lo planes of a K x cols column-major operand (``hi + lo`` reproduces the fp32 values)."""
+    """Operand planes of a K x cols column-major matrix ``x``.
+
+    Classic form: ``hi = rn_tf32(x)`` and ``lo = x - hi`` in fp32; a product is three tf32 MMAs per k-step
+    (``lo*hi + hi*lo + hi*hi``).  Mixed form (``hb`` / ``lb`` present, ``lo`` absent): ``hi`` as before plus
+    ``hb = bf16(x)`` and ``lb = bf16(x - hi)``; the two correction products then run as bf16 MMAs at twice the tf32
+    rate (their terms are 2^-11 of the main term, so bf16's 2^-9 leaves about 2^-20), with the same bytes per
+    element.  Both operands of a product must be of the same form.
+    """
 
     hi: Tensor
-    lo: Tensor
+    lo: Optional[Tensor]
     depth: int   # K: the contiguous, contracted extent
     cols: int
     ld: int
+    hb: Optional[Tensor] = None
+    lb: Optional[Tensor] = None
+    ld16: int = 0
+
+    @property
+    def mixed(self) -> bool:
+        return self.hb is not None
 
     @staticmethod
-    def empty(depth: int, cols: int, device) -> "Planes":
+    def empty(depth: int, cols: int, device, mixed: bool = False) -> "Planes":
         ld = max(4, round_up(depth, 4))
-        storage = torch.empty((2, max(1, cols), ld), dtype=torch.float32, device=device)
-        return Planes(storage[0], storage[1], depth, cols, ld)
+        if not mixed:
+            storage = torch.empty((2, max(1, cols), ld), dtype=torch.float32, device=device)
+            return Planes(storage[0], storage[1], depth, cols, ld)
+        ld16 = max(8, round_up(depth, 8))
+        hi = torch.empty((max(1, cols), ld), dtype=torch.float32, device=device)
+        halves = torch.empty((2, max(1, cols), ld16), dtype=torch.bfloat16, device=device)
+        return Planes(hi, None, depth, cols, ld, halves[0], halves[1], ld16)
 
     def sub(self, k0: int, c0: int, depth: int, cols: int) -> "Planes":
-        """Operand planes of the sub-matrix starting at row ``k0`` (a multiple of 4), column ``c0``."""
-        assert k0 % 4 == 0 and k0 + depth <= self.ld and c0 + cols <= self.hi.shape[0]
+        """Operand planes of the sub-matrix starting at row ``k0`` (a multiple of 4; of 8 for mixed planes),
+        column ``c0``."""
+        assert k0 % (8 if self.mixed else 4) == 0 and k0 + depth <= self.ld and c0 + cols <= self.hi.shape[0]
+        if self.mixed:
+            return Planes(self.hi[c0:, k0:], None, depth, cols, self.ld, self.hb[c0:, k0:], self.lb[c0:, k0:], self.ld16)
         return Planes(self.hi[c0:, k0:], self.lo[c0:, k0:], depth, cols, self.ld)
 
+    def low_pointers(self) -> dict:
+        """Pointer arguments of the low part for the native calls."""
+        if self.mixed:
+            return dict(lo=0, hb=self.hb.data_ptr(), lb=self.lb.data_ptr(), ld16=self.ld16)
+        return dict(lo=self.lo.data_ptr(), hb=0, lb=0, ld16=0)
+
     def dense(self) -> Tensor:
-        """The represented K x cols matrix (for tests)."""
-        return (self.hi[: self.cols, : self.depth] + self.lo[: self.cols, : self.depth]).T
+        """The represented K x cols matrix (for tests; to bf16 accuracy of the low part for mixed planes)."""
+        low = self.lb[: self.cols, : self.depth].float() if self.mixed else self.lo[: self.cols, : self.depth]
+        return (self.hi[: self.cols, : self.depth] + low).T
 
 
 SPLIT_ROUND_NEAREST = os.environ.get("SOAP_TP_SPLIT_NEAREST", "1") == "1"
 
 
 def split_planes(source: Tensor, *, transpose: bool = False, out: Optional[Planes] = None, scale: float = 1.0,
-                 nearest: Optional[bool] = None) -> Planes:
-    """Split a 2-D fp32 tensor (any strides) into operand planes.
+                 nearest: Optional[bool] = None, mixed: bool = False) -> Planes:
+    """Split a 2-D fp32 tensor (any strides) into operand planes (of the form of ``out``, else of ``mixed``).
 
     The operand is ``source`` itself (``depth = rows``) or, with ``transpose=True``, its transpose.
     """
@@ -188,10 +223,12 @@ def split_planes(source: Tensor, *, transpose: bool = False, out: Optional[Plane
     if transpose:
         rows, cols, s_i, s_j = cols, rows, s_j, s_i
     if out is None:
-        out = Planes.empty(rows, cols, source.device)
+        out = Planes.empty(rows, cols, source.device, mixed=mixed)
     assert out.depth == rows and out.cols == cols
-    _C.split_planes(source.data_ptr(), s_i, s_j, out.hi.data_ptr(), out.lo.data_ptr(), out.ld, rows, cols,
-                    float(scale), int(SPLIT_ROUND_NEAREST if nearest is None else nearest), _stream())
+    low = out.low_pointers()
+    _C.split_planes(source.data_ptr(), s_i, s_j, out.hi.data_ptr(), low["lo"], out.ld, rows, cols,
+                    float(scale), int(SPLIT_ROUND_NEAREST if nearest is None else nearest), _stream(),
+                    hb=low["hb"], lb=low["lb"], ld16=low["ld16"])
     _count("split_planes_kernel")
     return out
 
@@ -237,10 +274,20 @@ def gemm(
         else:
             assert out.stride(0) == 1 or out.shape[0] == 1
             ldc = out_ld if out_ld is not None else (out.stride(1) if out.shape[1] > 1 else max(1, out.shape[0]))
+    if a.mixed != b.mixed:
+        raise ValueError("both operands of a product must be classic planes or both mixed planes.")
     chi = clo = ldp = 0
+    mixed_arguments = {}
+    if a.mixed:
+        mixed_arguments.update(a_hb=a.hb.data_ptr(), a_lb=a.lb.data_ptr(), lda16=a.ld16, b_hb=b.hb.data_ptr(),
+                               b_lb=b.lb.data_ptr(), ldb16=b.ld16)
     if out_planes is not None:
         assert batch is not None or (out_planes.depth == M and out_planes.cols == N)
-        chi, clo, ldp = out_planes.hi.data_ptr(), out_planes.lo.data_ptr(), out_planes.ld
+        low = out_planes.low_pointers()
+        chi, clo, ldp = out_planes.hi.data_ptr(), low["lo"], out_planes.ld
+        if out_planes.mixed:
+            assert beta == 0.0, "mixed output planes cannot be read-modify-written"
+            mixed_arguments.update(Chb=low["hb"], Clb=low["lb"], ldp16=low["ld16"])
     mom = var = ldm = ldv = 0
     b1 = b2 = eps = ibc1 = isbc2 = 0.0
     if mode == EPI_ADAM:
@@ -251,10 +298,10 @@ def gemm(
         b1, b2, eps = adam["beta1"], adam["beta2"], adam["eps"]
         ibc1, isbc2 = 1.0 / adam["bias_correction1"], 1.0 / math.sqrt(adam["bias_correction2"])
     status = status_word(a.hi.device)
-    _C.gemm_tf32x3(a.hi.data_ptr(), a.lo.data_ptr(), a.ld, b.hi.data_ptr(), b.lo.data_ptr(), b.ld, M, N, K,
+    _C.gemm_tf32x3(a.hi.data_ptr(), a.low_pointers()["lo"], a.ld, b.hi.data_ptr(), b.low_pointers()["lo"], b.ld, M, N, K,
                    mode, 2 if lower_of_grid is not None else int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
                    mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, int(k_splits), int(split_stride), status.data_ptr(),
-                   _stream(), **_batch_arguments(a, b, batch), **_triangle_arguments(lower_of_grid))
+                   _stream(), **_batch_arguments(a, b, batch), **_triangle_arguments(lower_of_grid), **mixed_arguments)
     mark_written(out, momentum, variance)
     _count("gemm_tf32x3_kernel")
 

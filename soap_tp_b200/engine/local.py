@@ -44,8 +44,8 @@ class BasisPlanes:
         view = Q[:size, :size]
         if self.plain is not None and (self.plain.depth != size or self.plain.hi.device != Q.device):
             self.plain = self.transposed = None   # the address was recycled by a tensor of another size
-        self.plain = k.split_planes(view, out=self.plain)
-        self.transposed = k.split_planes(view, transpose=True, out=self.transposed)
+        self.plain = k.split_planes(view, out=self.plain, mixed=k.MIXED_CORRECTIONS)
+        self.transposed = k.split_planes(view, transpose=True, out=self.transposed, mixed=k.MIXED_CORRECTIONS)
         self.key = (Q.data_ptr(), Q._version, size)
 
 
@@ -73,12 +73,17 @@ def context_for(state: MutableMapping[str, Any]) -> ParameterContext:
     return ctx
 
 
+CLASSIC_TAGS = {"P", "Qtmp"}      # operands of the power iteration, which feeds the QR: always 3xTF32
+
+
 def workspace_planes(tag: str, depth: int, cols: int, device) -> k.Planes:
-    """Scratch operand planes shared by every parameter of the same shape on ``device``."""
-    key = (tag, depth, cols, str(device))
+    """Scratch operand planes shared by every parameter of the same shape on ``device``.  The operands of the
+    optimizer-step products are mixed planes (``kernels.Planes``) unless that is switched off."""
+    mixed = k.MIXED_CORRECTIONS and tag not in CLASSIC_TAGS
+    key = (tag, depth, cols, str(device), mixed)
     planes = _WORKSPACES.get(key)
     if planes is None:
-        planes = k.Planes.empty(depth, cols, device)
+        planes = k.Planes.empty(depth, cols, device, mixed=mixed)
         _WORKSPACES[key] = planes
     return planes
 

@@ -112,3 +112,63 @@ def test_split_epilogue_chain_and_adam():
     assert _rel(mt.cpu(), em) < 2e-6 and _rel(vt.cpu(), ev) < 6e-6
     assert _rel(y_planes.dense().cpu(), eu) < 1e-5
     assert _rel(proj.cpu(), eu) < 1e-5          # plain copy of the update
+
+
+MIXED_SHAPES = [(32, 128, 128), (64, 128, 256), (200, 130, 70), (40, 8, 8), (512, 384, 640), (1000, 257, 300),
+                (4096, 256, 512), (8192, 512, 512)]
+
+
+@pytest.mark.parametrize("K,M,N", MIXED_SHAPES)
+def test_mixed_corrections_match_fp64(K, M, N):
+    """The accuracy gate of the mixed form (correction products as bf16 MMAs): still fp32-class against fp64,
+    within a factor of the three-tf32-MMA form, at every depth up to the benchmark's 8192."""
+    from soap_tp_b200.engine import kernels as k
+
+    a, b = _operands(K, M, N, 11)
+    expected = a.double().T @ b.double()
+    classic = torch.empty(N, M, device="cuda").T
+    k.gemm(k.split_planes(a.cuda()), k.split_planes(b.cuda()), out=classic)
+    am, bm = k.split_planes(a.cuda(), mixed=True), k.split_planes(b.cuda(), mixed=True)
+    assert am.mixed and am.lo is None
+    assert float((am.dense().cpu() - a).abs().max()) <= 2.0 ** -18 * float(a.abs().max())     # hi + bf16(lo)
+    mixed = torch.empty(N, M, device="cuda").T
+    k.gemm(am, bm, out=mixed)
+    k.check_status()
+    error_classic, error_mixed = _rel(classic.cpu(), expected), _rel(mixed.cpu(), expected)
+    print(f"K={K}: 3xTF32 {error_classic:.2e}, tf32 + 2 bf16 corrections {error_mixed:.2e}")
+    assert error_mixed < 2e-6, error_mixed
+    assert error_mixed < 8 * max(error_classic, 1e-7)
+
+
+def test_mixed_output_planes_and_adam_epilogue():
+    """Epilogues that write the operand of the next product in the mixed form: split, and Adam in the eigenbasis."""
+    from soap_tp_b200.engine import kernels as k
+
+    K, M, N = 256, 384, 200
+    a, b = _operands(K, M, N, 12)
+    expected = a.double().T @ b.double()
+    am, bm = k.split_planes(a.cuda(), mixed=True), k.split_planes(b.cuda(), mixed=True)
+    out_planes = k.Planes.empty(M, N, "cuda", mixed=True)
+    plain = torch.empty(N, M, device="cuda").T
+    k.gemm(am, bm, mode=k.EPI_SPLIT, out_planes=out_planes, out=plain)
+    assert _rel(plain.cpu(), expected) < 2e-6
+    assert _rel(out_planes.dense().cpu(), expected) < 1e-5                     # hi + bf16(lo)
+    assert _rel(out_planes.hb[:N, :M].float().T.cpu(), expected) < 5e-3        # bf16(value)
+    # chained: the mixed planes are the operand of the next product
+    c = torch.randn(M, 96, generator=torch.Generator().manual_seed(13))
+    chained = torch.empty(96, N, device="cuda").T
+    k.gemm(out_planes, k.split_planes(c.cuda(), mixed=True), out=chained)
+    assert _rel(chained.cpu(), expected.T @ c.double()) < 3e-6
+    # Adam epilogue, update as mixed planes
+    momentum, variance = torch.zeros(N, M, device="cuda").T, torch.zeros(N, M, device="cuda").T
+    adam = dict(beta1=0.9, beta2=0.99, eps=1e-8, bias_correction1=0.1, bias_correction2=0.01)
+    update = k.Planes.empty(M, N, "cuda", mixed=True)
+    k.gemm(am, bm, mode=k.EPI_ADAM, out_planes=update, momentum=momentum, variance=variance, adam=adam)
+    k.check_status()
+    m = 0.1 * expected
+    v = 0.01 * expected * expected
+    want = (m / 0.1) / (v.sqrt() / 0.1 + 1e-8)
+    assert _rel(momentum.cpu(), m) < 2e-6
+    assert _rel(update.dense().cpu(), want) < 1e-4
+    with pytest.raises(ValueError, match="both operands"):
+        k.gemm(am, k.split_planes(b.cuda()), out=plain)
