@@ -41,8 +41,8 @@ PYBIND11_MODULE(_C, m) {
          uint64_t stream, int batches, int a_k_step, int a_row_step, int b_k_step, int b_row_step,
          int64_t c_batch_stride, int64_t a_k_total, int64_t a_rows_total, int64_t b_k_total, int64_t b_rows_total,
          uint64_t remap, uint64_t C2hi, uint64_t C2lo, int64_t ld2, int m_limit, int o1_row_start, int tri_nb,
-         int tri_pr, int tri_Pr, int tri_pc, int tri_Pc, int tri_m0, int tri_n0, uint64_t a_hb, uint64_t a_lb,
-         int64_t lda16, uint64_t b_hb, uint64_t b_lb, int64_t ldb16, uint64_t Chb, uint64_t Clb, int64_t ldp16) {
+         int tri_pr, int tri_Pr, int tri_pc, int tri_Pc, int tri_m0, int tri_n0, uint64_t a_hl, int64_t lda16,
+         uint64_t b_hl, int64_t ldb16, uint64_t Chl, int64_t ldp16) {
         GemmOperands ops{};
         ops.a_hi = ptr<const float>(a_hi); ops.a_lo = ptr<const float>(a_lo); ops.lda = lda;
         ops.b_hi = ptr<const float>(b_hi); ops.b_lo = ptr<const float>(b_lo); ops.ldb = ldb;
@@ -64,9 +64,9 @@ PYBIND11_MODULE(_C, m) {
         prob.ld2 = ld2; prob.m_limit = m_limit; prob.o1_row_start = o1_row_start;
         prob.tri_nb = tri_nb > 0 ? tri_nb : 1; prob.tri_pr = tri_pr; prob.tri_Pr = tri_Pr > 0 ? tri_Pr : 1;
         prob.tri_pc = tri_pc; prob.tri_Pc = tri_Pc > 0 ? tri_Pc : 1; prob.tri_m0 = tri_m0; prob.tri_n0 = tri_n0;
-        ops.a_hb = ptr<const uint16_t>(a_hb); ops.a_lb = ptr<const uint16_t>(a_lb); ops.lda16 = lda16;
-        ops.b_hb = ptr<const uint16_t>(b_hb); ops.b_lb = ptr<const uint16_t>(b_lb); ops.ldb16 = ldb16;
-        prob.Chb = ptr<uint16_t>(Chb); prob.Clb = ptr<uint16_t>(Clb); prob.ldp16 = ldp16;
+        ops.a_hl = ptr<const uint16_t>(a_hl); ops.lda16 = lda16;
+        ops.b_hl = ptr<const uint16_t>(b_hl); ops.ldb16 = ldb16;
+        prob.Chl = ptr<uint16_t>(Chl); prob.ldp16 = ldp16;
         py::gil_scoped_release release;
         gemm_tf32x3(ops, prob, ptr<int>(status), stream_of(stream));
       },
@@ -80,8 +80,8 @@ PYBIND11_MODULE(_C, m) {
       py::arg("a_rows_total") = 0, py::arg("b_k_total") = 0, py::arg("b_rows_total") = 0, py::arg("remap") = 0,
       py::arg("C2hi") = 0, py::arg("C2lo") = 0, py::arg("ld2") = 0, py::arg("m_limit") = 0, py::arg("o1_row_start") = 0, py::arg("tri_nb") = 1, py::arg("tri_pr") = 0,
       py::arg("tri_Pr") = 1, py::arg("tri_pc") = 0, py::arg("tri_Pc") = 1, py::arg("tri_m0") = 0, py::arg("tri_n0") = 0,
-      py::arg("a_hb") = 0, py::arg("a_lb") = 0, py::arg("lda16") = 0, py::arg("b_hb") = 0, py::arg("b_lb") = 0,
-      py::arg("ldb16") = 0, py::arg("Chb") = 0, py::arg("Clb") = 0, py::arg("ldp16") = 0,
+      py::arg("a_hl") = 0, py::arg("lda16") = 0, py::arg("b_hl") = 0, py::arg("ldb16") = 0, py::arg("Chl") = 0,
+      py::arg("ldp16") = 0,
       "3xTF32 tcgen05 GEMM acc[m,n] = sum_k Za[k,m] Zb[k,n] with fused epilogue");
 
   m.def("gemm_simt",
@@ -101,13 +101,12 @@ PYBIND11_MODULE(_C, m) {
 
   m.def("split_planes",
         [](uint64_t src, int64_t s_i, int64_t s_j, uint64_t hi, uint64_t lo, int64_t ldo, int rows, int cols,
-           float scale, int nearest, uint64_t stream, uint64_t hb, uint64_t lb, int64_t ld16) {
+           float scale, int nearest, uint64_t stream, uint64_t hl, int64_t ld16) {
           split_planes(ptr<const float>(src), s_i, s_j, ptr<float>(hi), ptr<float>(lo), ldo, rows, cols, scale, nearest,
-                       stream_of(stream), ptr<uint16_t>(hb), ptr<uint16_t>(lb), ld16);
+                       stream_of(stream), ptr<uint16_t>(hl), ld16);
         },
         py::arg("src"), py::arg("s_i"), py::arg("s_j"), py::arg("hi"), py::arg("lo"), py::arg("ldo"), py::arg("rows"),
-        py::arg("cols"), py::arg("scale"), py::arg("nearest"), py::arg("stream"), py::arg("hb") = 0, py::arg("lb") = 0,
-        py::arg("ld16") = 0);
+        py::arg("cols"), py::arg("scale"), py::arg("nearest"), py::arg("stream"), py::arg("hl") = 0, py::arg("ld16") = 0);
 
   m.def("column_dot",
         [](uint64_t a, int64_t lda, uint64_t b, int64_t ldb, uint64_t out, int rows, int cols, uint64_t stream) {

@@ -109,14 +109,16 @@ __device__ __forceinline__ float load_source(const DistSource& src, int gi, int 
   return __ldcg(source_address(src, gi, gj));  // bypass L1: peers rewrite these buffers between launches
 }
 
-// Where an output is written as operand planes: hi (fp32) and either lo (fp32) or the bf16 pair hb, lb.
+// Where an output is written as operand planes: hi (fp32) and either lo (fp32) or the interleaved bf16 plane hl.
 struct PlaneOut {
   float* hi;
-  float* lo;          // null with hb: mixed planes; null without hb: plain copy into `hi`
-  uint16_t* hb;
-  uint16_t* lb;
-  int64_t d_j16;      // column pitch of the bf16 planes (elements)
+  float* lo;          // null with hl: mixed planes; null without hl: plain copy into `hi`
+  uint16_t* hl;
+  int64_t d_j16;      // column pitch of the bf16 plane (elements)
 };
+
+// Position of element k of hb inside a column of the interleaved bf16 plane (lb: 32 further); as in gemm.h.
+__device__ __forceinline__ int64_t plane16(int64_t k) { return ((k >> 5) << 6) | (k & 31); }
 
 __device__ __forceinline__ uint16_t bf16_bits_dev(float v) {
   const __nv_bfloat16 b = __float2bfloat16_rn(v);
@@ -156,11 +158,11 @@ dist_gather_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose
     if (i < rows_out && j < cols_out && (!upper_only || map_index(map_i, i) < map_index(map_j, j))) {
       const float x = tile[t][tx];
       const int64_t off = i * d_i + j * d_j;
-      if (out.hb) {
+      if (out.hl) {
         const float h = tf32_round_dev(x);
         out_hi[off] = h;
-        out.hb[i * d_i + j * out.d_j16] = bf16_bits_dev(x);
-        out.lb[i * d_i + j * out.d_j16] = bf16_bits_dev(x - h);
+        out.hl[plane16(i) + j * out.d_j16] = bf16_bits_dev(x);          // (mixed planes always have d_i == 1)
+        out.hl[plane16(i) + 32 + j * out.d_j16] = bf16_bits_dev(x - h);
       } else if (out_lo) {
         const float h = tf32_round_dev(x);
         out_hi[off] = h;
@@ -194,8 +196,8 @@ __device__ __forceinline__ void store_group(const PlaneOut& out, int64_t i, int6
   float* out_hi = out.hi;
   float* out_lo = out.lo;
   const int64_t off = i + j * d_j;
-  if (out.hb) {
-    const int64_t off16 = i + j * out.d_j16;
+  if (out.hl) {
+    const int64_t off16 = plane16(i) + j * out.d_j16;
     const float v[4] = {x.x, x.y, x.z, x.w};
     float h[4], l[4];
     for (int e = 0; e < 4; ++e) {
@@ -209,13 +211,13 @@ __device__ __forceinline__ void store_group(const PlaneOut& out, int64_t i, int6
       uint2 pb, pc;
       pb.x = *reinterpret_cast<const uint32_t*>(&b0); pb.y = *reinterpret_cast<const uint32_t*>(&b1);
       pc.x = *reinterpret_cast<const uint32_t*>(&c0); pc.y = *reinterpret_cast<const uint32_t*>(&c1);
-      *reinterpret_cast<uint2*>(out.hb + off16) = pb;
-      *reinterpret_cast<uint2*>(out.lb + off16) = pc;
+      *reinterpret_cast<uint2*>(out.hl + off16) = pb;
+      *reinterpret_cast<uint2*>(out.hl + off16 + 32) = pc;
     } else {
       for (int e = 0; e < limit; ++e) {
         out_hi[off + e] = h[e];
-        out.hb[off16 + e] = bf16_bits_dev(v[e]);
-        out.lb[off16 + e] = bf16_bits_dev(l[e]);
+        out.hl[off16 + e] = bf16_bits_dev(v[e]);
+        out.hl[off16 + 32 + e] = bf16_bits_dev(l[e]);
       }
     }
     return;
@@ -389,11 +391,11 @@ void register_comm(py::module_& m) {
   auto gather = [](uint64_t peers, int kind, int rows, int cols, int nb_r, int nb_c, int Pr, int Pc, int world, int ip, int iP,
            int inb, int ioff, uint64_t iperm, int jp, int jP, int jnb, int joff, uint64_t jperm, int transpose,
            int upper_only, int i_local_offset, int j_local_offset, uint64_t out_hi, uint64_t out_lo,
-           int64_t d_i, int64_t d_j, int rows_out, int cols_out, uint64_t stream, uint64_t out_hb, uint64_t out_lb,
-           int64_t d_j16) {
+           int64_t d_i, int64_t d_j, int rows_out, int cols_out, uint64_t stream, uint64_t out_hl, int64_t d_j16) {
           if (rows_out <= 0 || cols_out <= 0) return;
-          PlaneOut out{reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), reinterpret_cast<uint16_t*>(out_hb),
-                       reinterpret_cast<uint16_t*>(out_lb), d_j16};
+          PlaneOut out{reinterpret_cast<float*>(out_hi), reinterpret_cast<float*>(out_lo), reinterpret_cast<uint16_t*>(out_hl),
+                       d_j16};
+          if (out_hl != 0 && d_i != 1) throw std::invalid_argument("dist_gather: mixed planes are written with unit row pitch");
           DistSource src{reinterpret_cast<const float* const*>(peers), kind, rows, cols, nb_r, nb_c, Pr, Pc, world};
           IndexMap mi{ip, iP, inb, ioff, reinterpret_cast<const int64_t*>(iperm), i_local_offset};
           IndexMap mj{jp, jP, jnb, joff, reinterpret_cast<const int64_t*>(jperm), j_local_offset};
@@ -420,7 +422,7 @@ void register_comm(py::module_& m) {
           else if (kind == kRowShards) source_groups = (cols % 4 == 0);
           else source_groups = (world > 0 && (cols / world) % 4 == 0);
           const bool aligned_out = d_i == 1 && d_j % 4 == 0 && (out_hi % 16 == 0) && (out_lo % 16 == 0) &&
-                                   (out_hb == 0 || (d_j16 % 4 == 0 && out_hb % 8 == 0 && out_lb % 8 == 0));
+                                   (out_hl == 0 || (d_j16 % 4 == 0 && out_hl % 8 == 0));
           if (!upper_only && keeps_groups(along) && source_groups && aligned_out &&
               !g_force_scalar_gather) {
             if (read_i_fast) {
@@ -446,9 +448,9 @@ void register_comm(py::module_& m) {
                  int64_t d_j, int rows_out, int cols_out, uint64_t stream) {
           gather(peers, kind, rows, cols, nb_r, nb_c, Pr, Pc, world, ip, iP, inb, ioff, iperm, jp, jP, jnb, joff, jperm,
                  transpose, upper_only, i_local_offset, j_local_offset, out_hi, out_lo, d_i, d_j, rows_out, cols_out, stream,
-                 0, 0, 0);
+                 0, 0);
         });
-  // the same with mixed operand planes as the output: hi (fp32) plus the bf16 planes hb, lb (column pitch d_j16)
+  // the same with mixed operand planes as the output: hi (fp32) plus the interleaved bf16 plane (column pitch d_j16)
   m.def("dist_gather_mixed", gather);
 
   m.def("signal_flag", [](uint64_t flag, int value, uint64_t stream) {

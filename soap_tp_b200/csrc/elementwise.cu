@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 
 #include "elementwise.h"
+#include "gemm.h"
 
 namespace soapb200 {
 namespace {
@@ -74,12 +75,12 @@ __device__ __forceinline__ uint16_t bf16_bits(float v) {
   return *reinterpret_cast<const uint16_t*>(&b);
 }
 
-// With `hb` / `lb` (bf16 planes, pitch ld16) the low part is written as bf16(x) and bf16(x - hi) instead of `lo`:
-// the operand format of the GEMM's mixed-precision corrections.
+// With `hl` (interleaved bf16 plane, pitch ld16, see gemm.h) the low part is written there as bf16(x) and
+// bf16(x - hi) instead of `lo`: the operand format of the GEMM's mixed-precision corrections.
 __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restrict__ src, int64_t s_i, int64_t s_j,
                                                            float* __restrict__ hi, float* __restrict__ lo, int64_t ldo,
                                                            int rows, int cols, float scale, int nearest,
-                                                           uint16_t* __restrict__ hb, uint16_t* __restrict__ lb, int64_t ld16) {
+                                                           uint16_t* __restrict__ hl, int64_t ld16) {
   __shared__ float tile[32][33];
   const int i0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
   const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;  // 32 x 8
@@ -98,9 +99,10 @@ __global__ void __launch_bounds__(256) split_planes_kernel(const float* __restri
       const float x = tile[t][tx] * scale;
       const float h = tf32_hi(x, nearest);
       hi[i + j * ldo] = h;
-      if (hb != nullptr) {
-        hb[i + j * ld16] = bf16_bits(x);
-        lb[i + j * ld16] = bf16_bits(x - h);
+      if (hl != nullptr) {
+        const int64_t at = bf16_plane_index(i) + j * ld16;
+        hl[at] = bf16_bits(x);
+        hl[at + 32] = bf16_bits(x - h);
       } else {
         lo[i + j * ldo] = x - h;
       }
@@ -170,10 +172,10 @@ void adam_update(const float* g, int64_t ldg, float* m, int64_t ldm, float* v, i
 }
 
 void split_planes(const float* src, int64_t s_i, int64_t s_j, float* hi, float* lo, int64_t ldo, int rows, int cols,
-                  float scale, int nearest, cudaStream_t stream, uint16_t* hb, uint16_t* lb, int64_t ld16) {
+                  float scale, int nearest, cudaStream_t stream, uint16_t* hl, int64_t ld16) {
   if (rows <= 0 || cols <= 0) return;
   dim3 grid((rows + 31) / 32, (cols + 31) / 32);
-  split_planes_kernel<<<grid, 256, 0, stream>>>(src, s_i, s_j, hi, lo, ldo, rows, cols, scale, nearest, hb, lb, ld16);
+  split_planes_kernel<<<grid, 256, 0, stream>>>(src, s_i, s_j, hi, lo, ldo, rows, cols, scale, nearest, hl, ld16);
   check_launch("split_planes_kernel");
 }
 

@@ -11,11 +11,10 @@ void adam_update(const float* g, int64_t ldg, float* m, int64_t ldm, float* v, i
                  int rows, int cols, float beta1, float beta2, float eps, float inv_bc1, float inv_sqrt_bc2,
                  cudaStream_t stream);
 
-// hi/lo planes of out(i, j) = scale * src[i*s_i + j*s_j]; planes are column-major with pitch ldo.  With hb / lb
-// (bf16, pitch ld16 elements) the low part goes there as bf16(value) and bf16(value - hi) and `lo` is not written.
+// hi/lo planes of out(i, j) = scale * src[i*s_i + j*s_j]; planes are column-major with pitch ldo.  With `hl` (the
+// interleaved bf16 plane of gemm.h, pitch ld16 elements) the low part goes there and `lo` is not written.
 void split_planes(const float* src, int64_t s_i, int64_t s_j, float* hi, float* lo, int64_t ldo, int rows, int cols,
-                  float scale, int nearest, cudaStream_t stream, uint16_t* hb = nullptr, uint16_t* lb = nullptr,
-                  int64_t ld16 = 0);
+                  float scale, int nearest, cudaStream_t stream, uint16_t* hl = nullptr, int64_t ld16 = 0);
 
 // out[j] = sum_i a[i, j] * b[i, j] for column-major a, b (deterministic tree reduction per column).
 void column_dot(const float* a, int64_t lda, const float* b, int64_t ldb, float* out, int rows, int cols,

@@ -25,16 +25,19 @@ struct GemmOperands {
   // Extents of the whole operand buffers when a launch addresses sub-blocks of them per batch item
   // (0: the operand is exactly K x M, resp. K x N).
   int64_t a_k_total = 0, a_rows_total = 0, b_k_total = 0, b_rows_total = 0;
-  // Mixed-precision corrections (all four non-null selects them): bf16 planes hb ~ hi and lb ~ lo of each operand
-  // (pitches in bf16 elements, multiples of 8).  The two correction products hi*lo and lo*hi then run as
+  // Mixed-precision corrections (both non-null selects them): one bf16 plane per operand that holds, for every
+  // 32 elements of K, 32 values hb = bf16(x) followed by 32 values lb = bf16(x - hi) -- element k of hb at
+  // (k / 32) * 64 + k % 32, of lb 32 further (`bf16_plane_index`); pitches in bf16 elements, multiples of 64, and
+  // the elements past K in the last group are zero.  The two correction products hi*lo and lo*hi then run as
   // kind::f16 MMAs at twice the tf32 rate; a_lo and b_lo are not read.
-  const uint16_t* a_hb = nullptr;
-  const uint16_t* a_lb = nullptr;
+  const uint16_t* a_hl = nullptr;
   int64_t lda16 = 0;
-  const uint16_t* b_hb = nullptr;
-  const uint16_t* b_lb = nullptr;
+  const uint16_t* b_hl = nullptr;
   int64_t ldb16 = 0;
 };
+
+// Position of element k of hb inside a row of the interleaved bf16 plane (lb: 32 further).
+__host__ __device__ inline int64_t bf16_plane_index(int64_t k) { return ((k >> 5) << 6) | (k & 31); }
 
 struct GemmProblem {
   int M, N, K;
@@ -52,8 +55,7 @@ struct GemmProblem {
   float* Chi;
   float* Clo;
   int64_t ldp;
-  uint16_t* Chb;     // kEpiSplit / kEpiAdam with mixed output planes: bf16(value) and bf16(value - hi) instead of Clo
-  uint16_t* Clb;
+  uint16_t* Chl;     // kEpiSplit / kEpiAdam with mixed output planes: the interleaved bf16 plane instead of Clo
   int64_t ldp16;
   float* mom;
   float* var;

@@ -73,8 +73,7 @@ struct TileConfig {
 };
 
 struct alignas(64) GemmMaps {
-  CUtensorMap a_hi, a_lo, b_hi, b_lo;     // MIXED: a_lo / b_lo describe the bf16 plane hb
-  CUtensorMap a_lb, b_lb;                 // MIXED only: the bf16 plane lb
+  CUtensorMap a_hi, a_lo, b_hi, b_lo;     // MIXED: a_lo / b_lo describe the interleaved bf16 plane (hb | lb)
 };
 
 // Four consecutive rows of one column as bf16 (8 bytes).
@@ -140,10 +139,10 @@ __device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t
     if (prob.beta != 0.0f) v = fmaf(prob.beta, prob.Chi[off] + prob.Clo[off], v);  // planes hold the old value
     const float hi = tf32_round(v);
     prob.Chi[off] = hi;
-    if (prob.Chb) {
-      const int64_t off16 = m + static_cast<int64_t>(n) * prob.ldp16;
-      prob.Chb[off16] = bf16_bits(v);
-      prob.Clb[off16] = bf16_bits(v - hi);
+    if (prob.Chl) {
+      const int64_t off16 = bf16_plane_index(m) + static_cast<int64_t>(n) * prob.ldp16;
+      prob.Chl[off16] = bf16_bits(v);
+      prob.Chl[off16 + 32] = bf16_bits(v - hi);
     } else {
       prob.Clo[off] = v - hi;
     }
@@ -160,10 +159,10 @@ __device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t
       const int64_t off = m + static_cast<int64_t>(n) * prob.ldp;
       const float hi = tf32_round(u);
       prob.Chi[off] = hi;
-      if (prob.Chb) {
-        const int64_t off16 = m + static_cast<int64_t>(n) * prob.ldp16;
-        prob.Chb[off16] = bf16_bits(u);
-        prob.Clb[off16] = bf16_bits(u - hi);
+      if (prob.Chl) {
+        const int64_t off16 = bf16_plane_index(m) + static_cast<int64_t>(n) * prob.ldp16;
+        prob.Chl[off16] = bf16_bits(u);
+        prob.Chl[off16 + 32] = bf16_bits(u - hi);
       } else {
         prob.Clo[off] = u - hi;
       }
@@ -216,9 +215,10 @@ __device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t
       lo.v[i] = v - hi.v[i];
     }
     store4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp, hi);
-    if (prob.Chb) {
-      store4_bf16(prob.Chb + m + static_cast<int64_t>(n) * prob.ldp16, plain.v);
-      store4_bf16(prob.Clb + m + static_cast<int64_t>(n) * prob.ldp16, lo.v);
+    if (prob.Chl) {
+      uint16_t* dst = prob.Chl + bf16_plane_index(m) + static_cast<int64_t>(n) * prob.ldp16;
+      store4_bf16(dst, plain.v);
+      store4_bf16(dst + 32, lo.v);
     } else {
       store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
     }
@@ -238,9 +238,10 @@ __device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t
     store4(prob.var + m + static_cast<int64_t>(n) * prob.ldv, va);
     if (prob.Chi) {
       store4(prob.Chi + m + static_cast<int64_t>(n) * prob.ldp, hi);
-      if (prob.Chb) {
-        store4_bf16(prob.Chb + m + static_cast<int64_t>(n) * prob.ldp16, u.v);
-        store4_bf16(prob.Clb + m + static_cast<int64_t>(n) * prob.ldp16, lo.v);
+      if (prob.Chl) {
+        uint16_t* dst = prob.Chl + bf16_plane_index(m) + static_cast<int64_t>(n) * prob.ldp16;
+        store4_bf16(dst, u.v);
+        store4_bf16(dst + 32, lo.v);
       } else {
         store4(prob.Clo + m + static_cast<int64_t>(n) * prob.ldp, lo);
       }
@@ -270,8 +271,7 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
   }
   bool vector = rows == kBM && !(prob.symmetric == 2 && ((prob.tri_nb | prob.tri_m0) & 3) != 0);
   if constexpr (MODE == kEpiStore) vector = vector && aligned16(prob.C + c_shift, prob.ldc);
-  if (prob.Chb != nullptr)
-    vector = vector && (prob.ldp16 & 3) == 0 && ((reinterpret_cast<uintptr_t>(prob.Chb) | reinterpret_cast<uintptr_t>(prob.Clb)) & 7) == 0;
+  if (prob.Chl != nullptr) vector = vector && (prob.ldp16 & 3) == 0 && (reinterpret_cast<uintptr_t>(prob.Chl) & 7) == 0;
   if constexpr (MODE == kEpiSplit)
     vector = vector && aligned16(prob.Chi, prob.ldp) && aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);
   if constexpr (MODE == kEpiAdam)
@@ -411,10 +411,6 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
     tma_prefetch_descriptor(&maps.a_lo);
     tma_prefetch_descriptor(&maps.b_hi);
     tma_prefetch_descriptor(&maps.b_lo);
-    if constexpr (MIXED) {
-      tma_prefetch_descriptor(&maps.a_lb);
-      tma_prefetch_descriptor(&maps.b_lb);
-    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -447,21 +443,12 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
       const int batch = blockIdx.z;
       const int ka = k0 + batch * prob.a_k_step, kbb = k0 + batch * prob.b_k_step;
       const int ra = m0 + batch * prob.a_row_step, rb = n0 + batch * prob.b_row_step;
-      if constexpr (MIXED) {
-        // per operand: hi as fp32 (128-byte rows), then hb and lb as bf16 (64-byte rows): the same bytes as hi + lo
-        tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
-        tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka, ra);
-        tma_load_2d(stage + kBM * kRowBytes + kBM * (kRowBytes / 2), &maps.a_lb, &full_bar[s], ka, ra);
-        uint8_t* b_stage = stage + 2 * kBM * kRowBytes;
-        tma_load_2d(b_stage, &maps.b_hi, &full_bar[s], kbb, rb);
-        tma_load_2d(b_stage + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb, rb);
-        tma_load_2d(b_stage + BN * kRowBytes + BN * (kRowBytes / 2), &maps.b_lb, &full_bar[s], kbb, rb);
-      } else {
-        tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
-        tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka, ra);
-        tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], kbb, rb);
-        tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb, rb);
-      }
+      // MIXED: the second plane of each operand is the interleaved bf16 plane, 64 elements (128 bytes) per 32 of K
+      const int ka2 = MIXED ? 2 * ka : ka, kbb2 = MIXED ? 2 * kbb : kbb;
+      tma_load_2d(stage, &maps.a_hi, &full_bar[s], ka, ra);
+      tma_load_2d(stage + kBM * kRowBytes, &maps.a_lo, &full_bar[s], ka2, ra);
+      tma_load_2d(stage + 2 * kBM * kRowBytes, &maps.b_hi, &full_bar[s], kbb, rb);
+      tma_load_2d(stage + 2 * kBM * kRowBytes + BN * kRowBytes, &maps.b_lo, &full_bar[s], kbb2, rb);
     }
     if (*abort_flag) {
       // give copies that are still in flight time to land before the CTA's shared memory is released
@@ -490,21 +477,19 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
         const uint32_t stage = smem_u32(smem + s * Cfg::kStageBytes);
         if constexpr (MIXED) {
           constexpr uint32_t idesc16 = umma_idesc_bf16(kBM, BN);
-          constexpr int kHalf = kRowBytes / 2;
-          const uint32_t b_stage = stage + 2 * kBM * kRowBytes;
           const uint64_t a_hi = umma_desc_kmajor<kRowBytes>(stage);
-          const uint64_t a_hb = umma_desc_kmajor<kHalf>(stage + kBM * kRowBytes);
-          const uint64_t a_lb = umma_desc_kmajor<kHalf>(stage + kBM * kRowBytes + kBM * kHalf);
-          const uint64_t b_hi = umma_desc_kmajor<kRowBytes>(b_stage);
-          const uint64_t b_hb = umma_desc_kmajor<kHalf>(b_stage + BN * kRowBytes);
-          const uint64_t b_lb = umma_desc_kmajor<kHalf>(b_stage + BN * kRowBytes + BN * kHalf);
-          // the two correction products as bf16 MMAs (16 elements of K = 32 bytes each), then hi*hi in tf32
+          const uint64_t a_hl = umma_desc_kmajor<kRowBytes>(stage + kBM * kRowBytes);
+          const uint64_t b_hi = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes);
+          const uint64_t b_hl = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes + BN * kRowBytes);
+          // A 128-byte row of the bf16 plane: hb of the 32 k-elements in bytes 0..63, lb in bytes 64..127.  The two
+          // correction products as bf16 MMAs (16 elements of K = 32 bytes each), then hi*hi in tf32.
+          constexpr uint64_t kLb = 64 >> 4;
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
-            umma_bf16_ss(tmem_acc, a_lb + adv, b_hb + adv, idesc16, first ? 0u : 1u);
+            umma_bf16_ss(tmem_acc, a_hl + kLb + adv, b_hl + adv, idesc16, first ? 0u : 1u);      // lo * hi
             first = 0;
-            umma_bf16_ss(tmem_acc, a_hb + adv, b_lb + adv, idesc16, 1);
+            umma_bf16_ss(tmem_acc, a_hl + adv, b_hl + kLb + adv, idesc16, 1);                    // hi * lo
           }
 #pragma unroll
           for (int k = 0; k < kBK / 8; ++k) {
@@ -631,17 +616,19 @@ CUtensorMap make_operand_map(const float* base, int64_t K, int64_t rows, int64_t
   return map;
 }
 
-// K-contiguous bf16 matrix [rows][K] with row pitch ld (elements); box = 32 elements (64 bytes) x box_rows rows.
+// Interleaved bf16 plane of a K-contiguous operand: [rows][64 * ceil(K / 32)] elements with row pitch ld
+// (elements); box = 64 elements (128 bytes: hb and lb of one 32-element k-block) x box_rows rows.
 CUtensorMap make_bf16_map(const uint16_t* base, int64_t K, int64_t rows, int64_t ld, int box_rows) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) throw std::invalid_argument("bf16 operand plane must be 16-byte aligned");
-  if ((ld * 2) % 16 != 0) throw std::invalid_argument("bf16 operand plane pitch must be a multiple of 8 elements");
+  const int64_t extent = 64 * ((K + 31) / 32);
+  if (ld % 64 != 0 || ld < extent) throw std::invalid_argument("bf16 operand plane pitch must be a multiple of 64 elements covering K");
   CUtensorMap map;
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(extent), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(2 * kBK), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t elem[2] = {1, 1};
   CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(base), dims, strides, box,
-                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled (bf16) failed with code " + std::to_string(res));
   return map;
@@ -658,15 +645,11 @@ void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaS
   maps.a_hi = make_operand_map(ops.a_hi, a_k, a_rows, ops.lda, kBM);
   maps.b_hi = make_operand_map(ops.b_hi, b_k, b_rows, ops.ldb, BN);
   if constexpr (MIXED) {
-    maps.a_lo = make_bf16_map(ops.a_hb, a_k, a_rows, ops.lda16, kBM);
-    maps.a_lb = make_bf16_map(ops.a_lb, a_k, a_rows, ops.lda16, kBM);
-    maps.b_lo = make_bf16_map(ops.b_hb, b_k, b_rows, ops.ldb16, BN);
-    maps.b_lb = make_bf16_map(ops.b_lb, b_k, b_rows, ops.ldb16, BN);
+    maps.a_lo = make_bf16_map(ops.a_hl, a_k, a_rows, ops.lda16, kBM);
+    maps.b_lo = make_bf16_map(ops.b_hl, b_k, b_rows, ops.ldb16, BN);
   } else {
     maps.a_lo = make_operand_map(ops.a_lo, a_k, a_rows, ops.lda, kBM);
     maps.b_lo = make_operand_map(ops.b_lo, b_k, b_rows, ops.ldb, BN);
-    maps.a_lb = maps.a_lo;
-    maps.b_lb = maps.b_lo;
   }
   const int tiles_m = (prob.M + kBM - 1) / kBM;
   const int tiles_n = (prob.N + BN - 1) / BN;
@@ -685,7 +668,7 @@ void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, 
   // Wide tiles when there are enough of them to fill the 148 SMs; narrower tiles otherwise.
   const int64_t wide_tiles = static_cast<int64_t>((prob.M + kBM - 1) / kBM) * ((prob.N + 255) / 256);
   const bool wide = prob.N > 128 && wide_tiles >= 148 && !prob.force_narrow;
-  const bool mixed = ops.a_hb && ops.a_lb && ops.b_hb && ops.b_lb;
+  const bool mixed = ops.a_hl && ops.b_hl;
   if (mixed && kBK != 32) throw std::invalid_argument("gemm_tf32x3: mixed corrections need the 32-element k-block build");
 #define SOAP_GEMM_LAUNCH(MODE_)                                                                      \
   do {                                                                                               \

@@ -80,7 +80,7 @@ def dist_gather(src: Source, map_i: IndexMap, map_j: IndexMap, rows_out: int, co
         low = planes.low_pointers()
         hi, lo, d_i, d_j = planes.hi.data_ptr(), low["lo"], 1, planes.ld
         if planes.mixed:
-            extra = (low["hb"], low["lb"], low["ld16"])
+            extra = (low["hl"], low["ld16"])
     else:
         assert out is not None
         hi, lo = out.data_ptr(), 0

@@ -157,10 +157,11 @@ class Planes:
     """Operand planes of a K x cols column-major matrix ``x``.
 
     Classic form: ``hi = rn_tf32(x)`` and ``lo = x - hi`` in fp32; a product is three tf32 MMAs per k-step
-    (``lo*hi + hi*lo + hi*hi``).  Mixed form (``hb`` / ``lb`` present, ``lo`` absent): ``hi`` as before plus
-    ``hb = bf16(x)`` and ``lb = bf16(x - hi)``; the two correction products then run as bf16 MMAs at twice the tf32
-    rate (their terms are 2^-11 of the main term, so bf16's 2^-9 leaves about 2^-20), with the same bytes per
-    element.  Both operands of a product must be of the same form.
+    (``lo*hi + hi*lo + hi*hi``).  Mixed form (``hl`` present, ``lo`` absent): ``hi`` as before plus one bf16 plane
+    that holds, for every 32 elements of K, the 32 values ``hb = bf16(x)`` followed by the 32 values
+    ``lb = bf16(x - hi)`` (one 128-byte row per TMA box and k-block; elements past K are zero).  The two correction
+    products then run as bf16 MMAs at twice the tf32 rate (their terms are 2^-11 of the main term, so bf16's 2^-9
+    leaves about 2^-20), with the same bytes per element.  Both operands of a product must be of the same form.
     """
 
     hi: Tensor
@@ -168,13 +169,12 @@ class Planes:
     depth: int   # K: the contiguous, contracted extent
     cols: int
     ld: int
-    hb: Optional[Tensor] = None
-    lb: Optional[Tensor] = None
+    hl: Optional[Tensor] = None
     ld16: int = 0
 
     @property
     def mixed(self) -> bool:
-        return self.hb is not None
+        return self.hl is not None
 
     @staticmethod
     def empty(depth: int, cols: int, device, mixed: bool = False) -> "Planes":
@@ -182,28 +182,37 @@ class Planes:
         if not mixed:
             storage = torch.empty((2, max(1, cols), ld), dtype=torch.float32, device=device)
             return Planes(storage[0], storage[1], depth, cols, ld)
-        ld16 = max(8, round_up(depth, 8))
+        ld16 = 2 * round_up(max(1, depth), 32)
         hi = torch.empty((max(1, cols), ld), dtype=torch.float32, device=device)
-        halves = torch.empty((2, max(1, cols), ld16), dtype=torch.bfloat16, device=device)
-        return Planes(hi, None, depth, cols, ld, halves[0], halves[1], ld16)
+        hl = torch.zeros((max(1, cols), ld16), dtype=torch.bfloat16, device=device)     # zeros: the tail past K stays zero
+        return Planes(hi, None, depth, cols, ld, hl, ld16)
 
     def sub(self, k0: int, c0: int, depth: int, cols: int) -> "Planes":
-        """Operand planes of the sub-matrix starting at row ``k0`` (a multiple of 4; of 8 for mixed planes),
-        column ``c0``."""
-        assert k0 % (8 if self.mixed else 4) == 0 and k0 + depth <= self.ld and c0 + cols <= self.hi.shape[0]
+        """Operand planes of the sub-matrix starting at row ``k0`` (a multiple of 4; of 32 for mixed planes, whose
+        depth may only be shortened to a multiple of 32), column ``c0``."""
+        assert k0 + depth <= self.ld and c0 + cols <= self.hi.shape[0]
         if self.mixed:
-            return Planes(self.hi[c0:, k0:], None, depth, cols, self.ld, self.hb[c0:, k0:], self.lb[c0:, k0:], self.ld16)
+            assert k0 % 32 == 0 and (k0 + depth == self.depth or depth % 32 == 0)
+            return Planes(self.hi[c0:, k0:], None, depth, cols, self.ld, self.hl[c0:, 2 * k0:], self.ld16)
+        assert k0 % 4 == 0
         return Planes(self.hi[c0:, k0:], self.lo[c0:, k0:], depth, cols, self.ld)
 
     def low_pointers(self) -> dict:
         """Pointer arguments of the low part for the native calls."""
         if self.mixed:
-            return dict(lo=0, hb=self.hb.data_ptr(), lb=self.lb.data_ptr(), ld16=self.ld16)
-        return dict(lo=self.lo.data_ptr(), hb=0, lb=0, ld16=0)
+            return dict(lo=0, hl=self.hl.data_ptr(), ld16=self.ld16)
+        return dict(lo=self.lo.data_ptr(), hl=0, ld16=0)
+
+    def halves(self):
+        """(hb, lb) of mixed planes as ``cols x depth`` fp32 tensors (tests)."""
+        groups = self.hl[: max(1, self.cols)].view(max(1, self.cols), -1, 2, 32).float()
+        hb = groups[:, :, 0, :].reshape(max(1, self.cols), -1)[: self.cols, : self.depth]
+        lb = groups[:, :, 1, :].reshape(max(1, self.cols), -1)[: self.cols, : self.depth]
+        return hb, lb
 
     def dense(self) -> Tensor:
         """The represented K x cols matrix (for tests; to bf16 accuracy of the low part for mixed planes)."""
-        low = self.lb[: self.cols, : self.depth].float() if self.mixed else self.lo[: self.cols, : self.depth]
+        low = self.halves()[1] if self.mixed else self.lo[: self.cols, : self.depth]
         return (self.hi[: self.cols, : self.depth] + low).T
 
 
@@ -228,7 +237,7 @@ def split_planes(source: Tensor, *, transpose: bool = False, out: Optional[Plane
     low = out.low_pointers()
     _C.split_planes(source.data_ptr(), s_i, s_j, out.hi.data_ptr(), low["lo"], out.ld, rows, cols,
                     float(scale), int(SPLIT_ROUND_NEAREST if nearest is None else nearest), _stream(),
-                    hb=low["hb"], lb=low["lb"], ld16=low["ld16"])
+                    hl=low["hl"], ld16=low["ld16"])
     _count("split_planes_kernel")
     return out
 
@@ -279,15 +288,14 @@ def gemm(
     chi = clo = ldp = 0
     mixed_arguments = {}
     if a.mixed:
-        mixed_arguments.update(a_hb=a.hb.data_ptr(), a_lb=a.lb.data_ptr(), lda16=a.ld16, b_hb=b.hb.data_ptr(),
-                               b_lb=b.lb.data_ptr(), ldb16=b.ld16)
+        mixed_arguments.update(a_hl=a.hl.data_ptr(), lda16=a.ld16, b_hl=b.hl.data_ptr(), ldb16=b.ld16)
     if out_planes is not None:
         assert batch is not None or (out_planes.depth == M and out_planes.cols == N)
         low = out_planes.low_pointers()
         chi, clo, ldp = out_planes.hi.data_ptr(), low["lo"], out_planes.ld
         if out_planes.mixed:
             assert beta == 0.0, "mixed output planes cannot be read-modify-written"
-            mixed_arguments.update(Chb=low["hb"], Clb=low["lb"], ldp16=low["ld16"])
+            mixed_arguments.update(Chl=low["hl"], ldp16=low["ld16"])
     mom = var = ldm = ldv = 0
     b1 = b2 = eps = ibc1 = isbc2 = 0.0
     if mode == EPI_ADAM:

@@ -121,3 +121,44 @@ def test_dist_gather_against_index_restatement(case):
                          torch.cuda.current_stream().cuda_stream)
         torch.cuda.synchronize()
         assert torch.equal(out.cpu(), expected)
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_dist_gather_into_mixed_planes(transpose):
+    """The same pull with mixed operand planes as the output (hi in fp32, hb | lb interleaved in bf16): the 16-byte
+    kernels and the element-wise kernel must write identical planes, and the planes must represent the source."""
+    from soap_tp_b200.engine import kernels as k
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    shape, nb, Pr, Pc, world = (384, 512), 64, 2, 2, 4
+    dense = torch.randn(shape, generator=torch.Generator().manual_seed(3))
+    kind = 2 if not transpose else 0
+    buffers, table = _make_source(dense, kind, nb, Pr, Pc, world, device)
+    rows_out = shape[1] if transpose else shape[0]
+    extent_j = shape[0] if transpose else shape[1]
+    cols_out = _numroc(extent_j, nb, 1, 2)
+    index_j = _map(cols_out, 1, 2, nb, 0, None, 0)
+    expected = (dense.T if transpose else dense)[:, index_j]
+
+    def run():
+        out = k.Planes.empty(rows_out, cols_out, device, mixed=True)
+        low = out.low_pointers()
+        k._C.dist_gather_mixed(table.data_ptr(), kind, shape[0], shape[1], nb, nb, Pr, Pc, world, 0, 1, 1, 0, 0,
+                               1, 2, nb, 0, 0, int(transpose), 0, 0, 0, out.hi.data_ptr(), 0, 1, out.ld, rows_out, cols_out,
+                               torch.cuda.current_stream().cuda_stream, low["hl"], low["ld16"])
+        torch.cuda.synchronize()
+        return out
+
+    fast = run()
+    k._C.force_scalar_gather(True)
+    try:
+        slow = run()
+    finally:
+        k._C.force_scalar_gather(False)
+    assert torch.equal(fast.hi, slow.hi) and torch.equal(fast.hl, slow.hl)
+    hb, lb = fast.halves()
+    hi = fast.hi[:cols_out, :rows_out]
+    want = expected.T.to(device)
+    assert float((hi + lb - want).abs().max()) <= 2.0 ** -18 * float(want.abs().max())
+    assert float((hb - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max())
