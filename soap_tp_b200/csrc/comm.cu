@@ -192,10 +192,19 @@ __device__ __forceinline__ float4 load_group(const DistSource& src, bool transpo
   return v;
 }
 
-__device__ __forceinline__ void store_group(const PlaneOut& out, int64_t i, int64_t j, int64_t d_j, const float4& x, int limit) {
+// `keep`: bit e set = element e of the group is written (all four: 0xF).
+__device__ __forceinline__ void store_group(const PlaneOut& out, int64_t i, int64_t j, int64_t d_j, const float4& x, int limit,
+                                            unsigned keep = 0xFu) {
   float* out_hi = out.hi;
   float* out_lo = out.lo;
   const int64_t off = i + j * d_j;
+  if (keep != 0xFu) {
+    // a group cut by the triangle mask (plain copies only: the mirrored half of a symmetric matrix)
+    const float v[4] = {x.x, x.y, x.z, x.w};
+    for (int e = 0; e < limit; ++e)
+      if (keep & (1u << e)) out_hi[off + e] = v[e];
+    return;
+  }
   if (out.hl) {
     const int64_t off16 = plane16(i) + j * out.d_j16;
     const float v[4] = {x.x, x.y, x.z, x.w};
@@ -248,7 +257,7 @@ __device__ __forceinline__ void store_group(const PlaneOut& out, int64_t i, int6
 // pass, four passes (four columns) in flight per thread; no shared memory.
 constexpr int kCopyTileI = 128, kCopyTileJ = 32;
 __global__ void __launch_bounds__(256)
-dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, PlaneOut out,
+dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, int upper_only, PlaneOut out,
                           int64_t d_j, int rows_out, int cols_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int i = blockIdx.x * kCopyTileI + 4 * lane;
@@ -257,15 +266,22 @@ dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
   const int a = map_index(map_i, i);
   const int j0 = blockIdx.y * kCopyTileJ + warp;
   float4 v[4];
+  unsigned keep[4];
 #pragma unroll
   for (int pass = 0; pass < 4; ++pass) {
     const int j = j0 + 8 * pass;
-    if (j < cols_out) v[pass] = load_group(src, transpose != 0, a, map_index(map_j, j), limit);
+    keep[pass] = 0;
+    if (j < cols_out) {
+      const int b = map_index(map_j, j);
+      // with the triangle mask only entries whose mapped row index is below their mapped column index move
+      keep[pass] = upper_only ? ((a < b) | ((a + 1 < b) << 1) | ((a + 2 < b) << 2) | ((a + 3 < b) << 3)) : 0xFu;
+      if (keep[pass]) v[pass] = load_group(src, transpose != 0, a, b, limit);
+    }
   }
 #pragma unroll
   for (int pass = 0; pass < 4; ++pass) {
     const int j = j0 + 8 * pass;
-    if (j < cols_out) store_group(out, i, j, d_j, v[pass], limit);
+    if (keep[pass]) store_group(out, i, j, d_j, v[pass], limit, keep[pass]);
   }
 }
 
@@ -273,7 +289,7 @@ dist_gather_copy16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
 // as 16-byte groups along i.
 constexpr int kTurnTile = 64;
 __global__ void __launch_bounds__(256)
-dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, PlaneOut out,
+dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int transpose, int upper_only, PlaneOut out,
                           int64_t d_j, int rows_out, int cols_out) {
   __shared__ float tile[kTurnTile][kTurnTile + 1];   // [i][j]
   const int i0 = blockIdx.x * kTurnTile, j0 = blockIdx.y * kTurnTile;
@@ -288,7 +304,10 @@ dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
       const int i = i0 + line + 16 * pass;
       v[pass] = make_float4(0.f, 0.f, 0.f, 0.f);
       // the group runs along the SECOND mapped index here: swap the roles for load_group
-      if (i < rows_out && limit > 0) v[pass] = load_group(src, transpose == 0, b, map_index(map_i, i), limit);
+      if (i < rows_out && limit > 0) {
+        const int a = map_index(map_i, i);
+        if (!upper_only || a < b + 3) v[pass] = load_group(src, transpose == 0, b, a, limit);   // some element has a < b + e
+      }
     }
 #pragma unroll
     for (int pass = 0; pass < 4; ++pass) {
@@ -305,7 +324,12 @@ dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
     const int jl = line + 16 * pass, j = j0 + jl;
     if (j < cols_out) {
       const float4 x = make_float4(tile[4 * group][jl], tile[4 * group + 1][jl], tile[4 * group + 2][jl], tile[4 * group + 3][jl]);
-      store_group(out, i, j, d_j, x, limit);
+      unsigned keep = 0xFu;
+      if (upper_only) {
+        const int a = map_index(map_i, i), b = map_index(map_j, j);     // a .. a+3 are consecutive (4-aligned group)
+        keep = (a < b) | ((a + 1 < b) << 1) | ((a + 2 < b) << 2) | ((a + 3 < b) << 3);
+      }
+      if (keep) store_group(out, i, j, d_j, x, limit, keep);
     }
   }
 }
@@ -423,15 +447,16 @@ void register_comm(py::module_& m) {
           else source_groups = (world > 0 && (cols / world) % 4 == 0);
           const bool aligned_out = d_i == 1 && d_j % 4 == 0 && (out_hi % 16 == 0) && (out_lo % 16 == 0) &&
                                    (out_hl == 0 || (d_j16 % 4 == 0 && out_hl % 8 == 0));
-          if (!upper_only && keeps_groups(along) && source_groups && aligned_out &&
-              !g_force_scalar_gather) {
+          // the triangle mask needs 4-aligned groups along i to be consecutive global indices as well
+          const bool mask_ok = !upper_only || (out_lo == 0 && out_hl == 0 && keeps_groups(mi));
+          if (mask_ok && keeps_groups(along) && source_groups && aligned_out && !g_force_scalar_gather) {
             if (read_i_fast) {
               dim3 grid((rows_out + kCopyTileI - 1) / kCopyTileI, (cols_out + kCopyTileJ - 1) / kCopyTileJ);
-              dist_gather_copy16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, out, d_j, rows_out, cols_out);
+              dist_gather_copy16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, upper_only, out, d_j, rows_out, cols_out);
               check(cudaGetLastError(), "dist_gather_copy16_kernel");
             } else {
               dim3 grid((rows_out + kTurnTile - 1) / kTurnTile, (cols_out + kTurnTile - 1) / kTurnTile);
-              dist_gather_turn16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, out, d_j, rows_out, cols_out);
+              dist_gather_turn16_kernel<<<grid, 256, 0, cuda_stream>>>(src, mi, mj, transpose, upper_only, out, d_j, rows_out, cols_out);
               check(cudaGetLastError(), "dist_gather_turn16_kernel");
             }
             return;

@@ -162,3 +162,40 @@ def test_dist_gather_into_mixed_planes(transpose):
     want = expected.T.to(device)
     assert float((hi + lb - want).abs().max()) <= 2.0 ** -18 * float(want.abs().max())
     assert float((hb - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_dist_gather_triangle_mask(transpose):
+    """``upper_only`` (the pull of the mirrored half of a symmetric packed matrix): only entries whose mapped row
+    index is below their mapped column index are written, everything else keeps its value; the 16-byte kernels and
+    the element-wise kernel must agree bit for bit."""
+    from soap_tp_b200.engine import kernels as k
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    n, nb, Pr, Pc = 640, 64, 2, 2
+    dense = torch.randn(n, n, generator=torch.Generator().manual_seed(5))
+    buffers, table = _make_source(dense, 0, nb, Pr, Pc, 4, device)
+    pr, pc = 1, 0
+    lr, lc = _numroc(n, nb, pr, Pr), _numroc(n, nb, pc, Pc)
+    gi, gj = _map(lr, pr, Pr, nb, 0, None, 0), _map(lc, pc, Pc, nb, 0, None, 0)
+    source = dense.T if transpose else dense
+    expected = torch.full((lr, lc), -7.0)
+    mask = gi[:, None] < gj[None, :]
+    expected[mask] = source[gi[:, None], gj[None, :]][mask]
+
+    def run():
+        out = torch.full((lc, lr), -7.0, device=device).T
+        k._C.dist_gather(table.data_ptr(), 0, n, n, nb, nb, Pr, Pc, 4, pr, Pr, nb, 0, 0, pc, Pc, nb, 0, 0, int(transpose), 1,
+                         0, 0, out.data_ptr(), 0, 1, out.stride(1), lr, lc, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        return out.cpu()
+
+    fast = run()
+    k._C.force_scalar_gather(True)
+    try:
+        slow = run()
+    finally:
+        k._C.force_scalar_gather(False)
+    assert torch.equal(slow, expected)
+    assert torch.equal(fast, expected)
