@@ -335,13 +335,15 @@ dist_gather_turn16_kernel(DistSource src, IndexMap map_i, IndexMap map_j, int tr
 }
 
 // ---- cross-rank barrier ----------------------------------------------------------------------
-__global__ void barrier_kernel(int* const* pads, int rank, int world, int epoch, int* status, long long budget_ns) {
+// `slot0`: first word of this barrier's channel inside every pad (channels let barriers of different streams be in
+// flight at the same time without seeing each other's epochs).
+__global__ void barrier_kernel(int* const* pads, int rank, int world, int epoch, int* status, long long budget_ns, int slot0) {
   const int peer = threadIdx.x;
   if (peer >= world) return;
   __threadfence_system();
-  int* remote = pads[peer] + rank;
+  int* remote = pads[peer] + slot0 + rank;
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-  const int* mine = pads[rank] + peer;
+  const int* mine = pads[rank] + slot0 + peer;
   unsigned long long start, now;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
   for (;;) {
@@ -492,13 +494,14 @@ void register_comm(py::module_& m) {
         "Route every dist_gather through the element-wise kernel (cross-checks of the 16-byte paths)");
 
   m.def("device_barrier", [](uint64_t pads, int rank, int world, int epoch, uint64_t status, double budget_seconds,
-                             uint64_t stream) {
+                             uint64_t stream, int slot0) {
     if (world > 1024) throw std::invalid_argument("device_barrier supports at most 1024 ranks");
     barrier_kernel<<<1, ((world + 31) / 32) * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<int* const*>(pads), rank, world, epoch, reinterpret_cast<int*>(status),
-        static_cast<long long>(budget_seconds * 1e9));
+        static_cast<long long>(budget_seconds * 1e9), slot0);
     check(cudaGetLastError(), "barrier_kernel");
-  });
+  }, py::arg("pads"), py::arg("rank"), py::arg("world"), py::arg("epoch"), py::arg("status"), py::arg("budget_seconds"),
+     py::arg("stream"), py::arg("slot0") = 0);
 }
 
 }  // namespace soapb200

@@ -106,51 +106,72 @@ __device__ __forceinline__ float sum_over_ctas(const float* partials, int slot, 
   return total;
 }
 
+// Row ownership: row i of the matrix (and of the panel's [V | W] store) belongs to CTA i % G, slot i / G.  A CTA keeps
+// its rows of [V | W] in shared memory, so the row-wise phases never wait for L2; eight threads share a row.
+constexpr int kRowSlots = kThreads / 8;          // rows handled per pass of a row-wise phase
+constexpr int kStorePitch = kRowPitch + 1;       // floats per row of the shared store (odd: no bank conflicts)
+
+__device__ __forceinline__ float octet_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
 __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs a) {
-  extern __shared__ __align__(16) float v_s[];                 // [n]: the current Householder vector, zero above its first entry
-  __shared__ float red_w[kWarps][kRowPitch];     // per-warp partial sums of p = W^T v and q = V^T v
+  extern __shared__ __align__(16) float dyn[];   // v_s[n4] (the current Householder vector), then the row store
+  __shared__ float red_w[kWarps][kRowPitch];     // partial sums of p = W^T v and q = V^T v
   __shared__ float pq[kRowPitch];                // q in [0, kTB), p in [kTB, 2 kTB)
   __shared__ float rowj[kRowPitch];              // row j of [V | W] while column j is being reduced
   __shared__ float scratch[kWarps];
   __shared__ float T[kTB][kTB + 1];              // CTA 0: compact-WY factor of the panel
-  __shared__ float taus[kTB];
   __shared__ float bcast;
 
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-  const int G = gridDim.x;
+  const int G = gridDim.x, b = blockIdx.x;
   const int n = a.n;
   const int64_t lda = a.lda;
-  const int gid = blockIdx.x * kThreads + t;                 // this thread's first row
-  const int row_stride = G * kThreads;
-  const int gwarp = blockIdx.x * kWarps + warp, total_warps = G * kWarps;
+  const int slots = (n + G - 1) / G;                          // rows of this CTA (some may be past the end)
+  float* v_s = dyn;
+  float* store = dyn + ((n + 3) & ~3);                        // [slots][kStorePitch]
+  const int part = t & 7;                                     // which eighth of a row's coefficients
+  const int gwarp = b * kWarps + warp, total_warps = G * kWarps;
   const bool vec_ok = (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.A) & 15) == 0);
   unsigned int target = 0;
-  float* partial = a.partial + static_cast<int64_t>(blockIdx.x) * kPartialPitch;
+  float* partial = a.partial + static_cast<int64_t>(b) * kPartialPitch;
 
-  if (blockIdx.x == 0) {
+  if (b == 0)
     for (int idx = t; idx < kTB * (kTB + 1); idx += kThreads) (&T[0][0])[idx] = 0.f;
-    if (t < kTB) taus[t] = 0.f;
-  }
-  // rows of the [V | W] store start out as zeros for this panel (every thread clears the rows it owns)
-  for (int i = gid; i < n; i += row_stride)
-    for (int c = 0; c < kRowPitch; ++c) a.vw[static_cast<int64_t>(i) * kRowPitch + c] = 0.f;
+  for (int idx = t; idx < slots * kStorePitch; idx += kThreads) store[idx] = 0.f;
   if (t < kRowPitch) rowj[t] = 0.f;
   __syncthreads();
 
-  // Column update of column `j` (k-th of the panel) for the rows this thread owns, from the panel's reflectors so
-  // far (`rowj` holds row j of [V | W]): writes x, the diagonal entry and this CTA's part of |x[j+2:]|^2.
+  // This thread's share of sum_c<k ( V[i][c] * second[kTB + c] + W[i][c] * second[c] ) for the row in `slot`; the
+  // eight threads of the row add their shares with `octet_sum`, which every thread of the warp must reach.
+  auto pending = [&](int slot, int k, const float* second) {
+    const float* mine = store + slot * kStorePitch;
+    float acc = 0.f;
+    for (int c = part; c < k; c += 8) acc = fmaf(mine[c], second[kTB + c], fmaf(mine[kTB + c], second[c], acc));
+    return acc;
+  };
+
+  // Column update of column `j` (k-th of the panel) for this CTA's rows (`rowj` holds row j of [V | W]): writes x,
+  // the diagonal entry and this CTA's part of |x[j+2:]|^2.
   auto column_update = [&](int j, int k) {
     float sumsq = 0.f;
-    for (int i = gid; i < n; i += row_stride) {
-      if (i < j) continue;
-      float value = a.A[i + static_cast<int64_t>(j) * lda];
-      const float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
-      for (int c = 0; c < k; ++c) value -= mine[c] * rowj[kTB + c] + mine[kTB + c] * rowj[c];
-      if (i == j) {
-        a.d[j] = static_cast<double>(value);
-      } else {
-        a.x[i] = value;
-        if (i > j + 1) sumsq = fmaf(value, value, sumsq);
+    for (int s0 = 0; s0 < slots; s0 += kRowSlots) {
+      const int slot = s0 + (t >> 3);
+      const int i = slot * G + b;
+      const bool live = slot < slots && i >= j && i < n;
+      const float correction = octet_sum(live ? pending(slot, k, rowj) : 0.f);
+      if (live && part == 0) {
+        const float value = a.A[i + static_cast<int64_t>(j) * lda] - correction;
+        if (i == j) {
+          a.d[j] = static_cast<double>(value);
+        } else {
+          a.x[i] = value;
+          if (i > j + 1) sumsq = fmaf(value, value, sumsq);
+        }
       }
     }
     const float cta_sumsq = block_sum(sumsq, scratch);
@@ -178,22 +199,22 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
       v_s[i] = value;
     }
     __syncthreads();
-    // q_c = sum_i V[i][c] v_i and p_c = sum_i W[i][c] v_i over this CTA's rows: thread (value, group) walks every
-    // eighth row of the slab, so the loads of a warp are contiguous and nothing is shuffled
+    // q_c = sum_i V[i][c] v_i and p_c = sum_i W[i][c] v_i over this CTA's rows (thread = (coefficient, row group))
     {
       const int value = t % kRowPitch, group = t / kRowPitch;
       float acc = 0.f;
-      if (value % kTB < k) {
-        for (int base = blockIdx.x * kThreads; base < n; base += row_stride)
-          for (int r = group; r < kThreads; r += kThreads / kRowPitch) {
-            const int i = base + r;
-            if (i > j && i < n) acc = fmaf(__ldcg(&a.vw[static_cast<int64_t>(i) * kRowPitch + value]), v_s[i], acc);
-          }
-      }
+      if (value % kTB < k)
+        for (int slot = group; slot < slots; slot += kThreads / kRowPitch) {
+          const int i = slot * G + b;
+          if (i > j && i < n) acc = fmaf(store[slot * kStorePitch + value], v_s[i], acc);
+        }
       red_w[group][value] = acc;
     }
-    for (int i = gid; i < n; i += row_stride)
-      if (i > j) a.vw[static_cast<int64_t>(i) * kRowPitch + k] = v_s[i];
+    __syncthreads();
+    for (int slot = t; slot < slots; slot += kThreads) {         // V[:, k] = v for the own rows
+      const int i = slot * G + b;
+      if (i > j && i < n) store[slot * kStorePitch + k] = v_s[i];
+    }
     // y = A[j+1:, j+1:] v: warp per column, lanes along the (contiguous) rows; y.v on the way
     float yv = 0.f;
     {
@@ -235,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
         }
       }
     }
-    const float cta_yv = block_sum(yv, scratch);       // (its barriers also order red_w)
+    const float cta_yv = block_sum(yv, scratch);
     if (t < kRowPitch) {
       float total = 0.f;
       for (int g = 0; g < kThreads / kRowPitch; ++g) total += red_w[g][t];
@@ -264,14 +285,17 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
     for (int c = 0; c < k; ++c) qp = fmaf(pq[c], pq[kTB + c], qp);
     const float s = yv_raw - 2.f * qp;
     const float coef = -0.5f * tau * tau * s;
-    for (int i = gid; i < n; i += row_stride) {
-      if (i <= j) continue;
-      float value = __ldcg(&a.y[i]);
-      float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
-      for (int c = 0; c < k; ++c) value -= mine[c] * pq[kTB + c] + mine[kTB + c] * pq[c];
-      mine[kTB + k] = fmaf(tau, value, coef * v_s[i]);          // w = tau y' - (tau^2 / 2) (y'.v) v
+    for (int s0 = 0; s0 < slots; s0 += kRowSlots) {
+      const int slot = s0 + (t >> 3);
+      const int i = slot * G + b;
+      const bool live = slot < slots && i > j && i < n;
+      const float correction = octet_sum(live ? pending(slot, k, pq) : 0.f);      // V[i] . p + W[i] . q
+      if (live && part == 0) {
+        const float value = __ldcg(&a.y[i]) - correction;
+        store[slot * kStorePitch + kTB + k] = fmaf(tau, value, coef * v_s[i]);    // w = tau y' - (tau^2 / 2) (y'.v) v
+      }
     }
-    if (blockIdx.x == 0) {
+    if (b == 0) {
       // T[0:k, k] = -tau T[0:k, 0:k] q[0:k], T[k][k] = tau
       if (t < k) {
         float acc = 0.f;
@@ -280,19 +304,25 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
       }
       if (t == k) {
         T[k][k] = tau;
-        taus[k] = tau;
         a.tau[j] = tau;
         a.e[j] = static_cast<double>(beta);
       }
     }
+    __syncthreads();
+    // The row that the column after the next one needs from everybody is complete now up to this reflector: its
+    // owner publishes it (two barriers lie between this store and its readers).
+    {
+      const int future = j + 2;
+      if (k + 2 < a.nb && future < n && future % G == b && t < kRowPitch)
+        a.vw[((k + 2) & 1) * kRowPitch + t] = store[(future / G) * kStorePitch + t];
+    }
     if (k + 1 < a.nb) {
-      // row j+1 of [V | W] for the next column: stored entries for the older reflectors, rebuilt ones for this one
-      // (v starts with 1 in row j+1; its w entry follows from y[j+1], p, q, which every CTA has)
+      // row j+1 of [V | W] for the next column: published entries for the older reflectors, rebuilt ones for this
+      // one (v starts with 1 in row j+1; its w entry follows from y[j+1], p, q, which every CTA has)
       const int jn = j + 1;
-      __syncthreads();                            // rowj is still read by nobody; pq is complete
       if (t < kRowPitch) {
         const int c = t % kTB;
-        rowj[t] = (c < k) ? __ldcg(&a.vw[static_cast<int64_t>(jn) * kRowPitch + t]) : 0.f;
+        rowj[t] = (c < k) ? __ldcg(&a.vw[((k + 1) & 1) * kRowPitch + t]) : 0.f;
       }
       __syncthreads();
       if (t == 0) {
@@ -306,51 +336,46 @@ __global__ void __launch_bounds__(kThreads, 1) sytrd_panel_kernel(SytrdPanelArgs
     }
     if (!grid_barrier(a.barrier, target, a.status)) { alive = false; break; }
   }
-  if (!alive) return;      // (the loop's last barrier made every row of the store visible to all CTAs)
+  if (!alive) return;
 
   const int next = a.j0 + a.nb;                    // first row / column of the trailing matrix
-  // ---- outputs ----
-  if (a.last) {
+  // ---- outputs (every CTA for its own rows) ----
+  if (a.last && (n - 1) % G == b && t == 0) {
     // d[n-1] = A[n-1][n-1] minus the panel's pending update of that entry
-    if (gid == 0) {
-      const int i = n - 1;
-      float value = a.A[i + static_cast<int64_t>(i) * lda];
-      const float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
-      for (int c = 0; c < a.nb; ++c) value -= 2.f * __ldcg(&mine[c]) * __ldcg(&mine[kTB + c]);
-      a.d[i] = static_cast<double>(value);
-    }
+    const int i = n - 1;
+    const float* mine = store + (i / G) * kStorePitch;
+    float value = a.A[i + static_cast<int64_t>(i) * lda];
+    for (int c = 0; c < a.nb; ++c) value -= 2.f * mine[c] * mine[kTB + c];
+    a.d[i] = static_cast<double>(value);
   }
-  for (int i = gid; i < n; i += row_stride) {
-    const float* mine = &a.vw[static_cast<int64_t>(i) * kRowPitch];
+  for (int idx = t; idx < slots * kRowPitch; idx += kThreads) {
+    const int slot = idx / kRowPitch, c = idx % kRowPitch;
+    const int i = slot * G + b;
+    if (i >= n) continue;
+    const float* mine = store + slot * kStorePitch;
     if (i >= next) {
       // operand planes of the trailing update: Za row = [V | W], Zb row = [W | V]
       const int64_t base = static_cast<int64_t>(i - next) * kRowPitch;
-      for (int c = 0; c < kRowPitch; ++c) {
-        const float va = __ldcg(&mine[c]);
-        const float vb = __ldcg(&mine[(c + kTB) % kRowPitch]);
-        const float ha = tf32_rn(va), hb = tf32_rn(vb);
-        a.za_hi[base + c] = ha;
-        a.za_lo[base + c] = va - ha;
-        a.zb_hi[base + c] = hb;
-        a.zb_lo[base + c] = vb - hb;
-      }
+      const float va = mine[c], vb = mine[(c + kTB) % kRowPitch];
+      const float ha = tf32_rn(va), hb = tf32_rn(vb);
+      a.za_hi[base + c] = ha;
+      a.za_lo[base + c] = va - ha;
+      a.zb_hi[base + c] = hb;
+      a.zb_lo[base + c] = vb - hb;
     }
-    if (i >= a.j0) {
+    if (i >= a.j0 && c < a.nb) {
       // V and V^T of the panel, rows j0 .. n-1 (row j0 is all zeros: every reflector starts below it; starting
       // there keeps the planes' first row on a 16-byte boundary)
       const int local = i - a.j0;
-      for (int c = 0; c < a.nb; ++c) {
-        const float v = __ldcg(&mine[c]);
-        const float h = tf32_rn(v);
-        a.v_hi[local + static_cast<int64_t>(c) * a.ldv] = h;
-        a.v_lo[local + static_cast<int64_t>(c) * a.ldv] = v - h;
-        a.vt_hi[c + static_cast<int64_t>(local) * a.ldvt] = h;
-        a.vt_lo[c + static_cast<int64_t>(local) * a.ldvt] = v - h;
-      }
+      const float v = mine[c];
+      const float h = tf32_rn(v);
+      a.v_hi[local + static_cast<int64_t>(c) * a.ldv] = h;
+      a.v_lo[local + static_cast<int64_t>(c) * a.ldv] = v - h;
+      a.vt_hi[c + static_cast<int64_t>(local) * a.ldvt] = h;
+      a.vt_lo[c + static_cast<int64_t>(local) * a.ldvt] = v - h;
     }
   }
-  if (blockIdx.x == 0) {
-    __syncthreads();
+  if (b == 0) {
     for (int idx = t; idx < kTB * kTB; idx += kThreads) {
       const int r = idx % kTB, c = idx / kTB;
       const float v = (r < a.nb && c < a.nb) ? T[r][c] : 0.f;
@@ -450,12 +475,14 @@ void sytrd_panel(const SytrdPanelArgs& args, cudaStream_t stream) {
   int device = 0, sms = 0;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  const size_t smem = static_cast<size_t>(args.n + 4) * sizeof(float);
-  static PerDeviceOnce configured;
-  // the largest matrix decides the limit; 64 KB of dynamic shared memory covers n = 16384
-  allow_dynamic_smem(reinterpret_cast<const void*>(sytrd_panel_kernel), 96 * 1024, configured, "sytrd_panel");
-  if (smem > 96 * 1024) throw std::invalid_argument("sytrd_panel: matrix side above 24576 is not supported");
   const int ctas = sms > 0 ? sms : 1;     // one CTA per SM: all of them are resident, as the grid barrier needs
+  // the Householder vector (n floats) and this CTA's rows of the panel's [V | W] store (ceil(n / CTAs) x 65 floats)
+  const size_t smem = (static_cast<size_t>((args.n + 3) & ~3) + static_cast<size_t>((args.n + ctas - 1) / ctas) * (2 * kTB + 1)) *
+                      sizeof(float);
+  constexpr size_t kSmemLimit = 160 * 1024;
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(sytrd_panel_kernel), kSmemLimit, configured, "sytrd_panel");
+  if (smem > kSmemLimit) throw std::invalid_argument("sytrd_panel: the matrix side is too large for one CTA's shared memory");
   cudaError_t err = cudaMemsetAsync(args.barrier, 0, sizeof(unsigned int), stream);
   if (err != cudaSuccess) throw std::runtime_error(std::string("sytrd_panel memset: ") + cudaGetErrorString(err));
   SytrdPanelArgs copy = args;

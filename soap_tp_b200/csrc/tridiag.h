@@ -13,7 +13,7 @@ struct SytrdPanelArgs {
   int n;
   int j0;              // first column of the panel
   int nb;              // columns in this launch (<= 32), j0 + nb <= n - 1
-  float* vw;           // [n][64] scratch: row i holds V[i][0:32] | W[i][0:32] of this panel
+  float* vw;           // [2][64] scratch: the row of [V | W] that the next columns need from every CTA (double buffered)
   float* x;            // [n] scratch
   float* y;            // [n] scratch
   float* partial;      // [SM count][72] scratch

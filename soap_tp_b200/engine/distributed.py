@@ -38,6 +38,8 @@ KIND_BLOCK_CYCLIC, KIND_ROW_SHARDS, KIND_COL_SHARDS = 0, 1, 2
 PIPELINE_GATHERS = os.environ.get("SOAP_TP_PIPELINE_GATHERS", "0") == "1"
 # SOAP_TP_DISTRIBUTED_QR=0: every factorisation runs on one leader rank even when its group has more ranks
 DISTRIBUTED_QR = os.environ.get("SOAP_TP_DISTRIBUTED_QR", "1") != "0"
+# SOAP_TP_OVERLAP_GRAM=0: the Gram EMAs run after the rotations on the same stream instead of beside them
+OVERLAP_GRAM = os.environ.get("SOAP_TP_OVERLAP_GRAM", "1") != "0"
 # output tiles a chunk must keep (about one wave of the 148 SMs); tests lower it to chunk small problems
 PIPELINE_MIN_TILES = max(1, int(os.environ.get("SOAP_TP_PIPELINE_MIN_TILES", "120")))
 
@@ -202,7 +204,12 @@ class GridEngine:
         entry.update(key=(Q._version, size), plain=plain, transposed=transposed)
         return plain, transposed
 
-    # ---- two chained stationary-C products ---------------------------------------------------
+    def side_stream(self) -> "torch.cuda.Stream":
+        """The stream on which work that is independent of the rotations (the Gram EMAs) runs beside them."""
+        if not hasattr(self, "_side_stream"):
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        return self._side_stream
+
     # ---- gather / product pipelining ------------------------------------------------------------
     def _pipeline_streams(self):
         if not hasattr(self, "_gather_stream"):
@@ -464,7 +471,7 @@ def _gram_from_source(e: GridEngine, source: Source, shape, preconditioner: Tens
     e.gather_then_multiply(source, e.row_map(), depth, lr, a, rows_window, transpose=transpose, other_cols=lc)
 
 
-def _mirror_upper(e: GridEngine, items) -> None:
+def _mirror_upper(e: GridEngine, items, channel: int = 0) -> None:
     """Complete symmetric packed matrices whose lower triangles were just computed.
 
     ``items``: ``(tag, matrix, size)``.  Every rank publishes its packed block, and after one barrier
@@ -473,7 +480,7 @@ def _mirror_upper(e: GridEngine, items) -> None:
     only after a later barrier of the caller.
     """
     sources = [e.stage_packed(f"gram_{tag}", matrix, (size, size)) for tag, matrix, size in items]
-    e.comm.barrier()
+    e.comm.barrier(channel=channel)
     for source, (tag, matrix, size) in zip(sources, items):
         lr, lc = e.rows_of(size), e.cols_of(size)
         if lr and lc:
@@ -738,11 +745,38 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
     bias2 = 1.0 - beta2**step
     adam = dict(beta1=beta1, beta2=beta2, eps=eps / math.sqrt(bias2),
                 bias_correction1=1.0 - beta1**step, bias_correction2=bias2)
+    main = torch.cuda.current_stream(device)
+    x_panel = e.planes("x_panel", rows, e.rows_of(cols))   # X[:, my row class]: forward rotation and right Gram
+    with TIMER.stage("pull_gradient_panel", device):
+        if x_panel.cols > 0:
+            dist_gather(shard_source, IDENTITY, e.row_map(), rows, x_panel.cols, planes=x_panel)
+
+    def gram_updates(channel: int) -> None:
+        # Gram EMAs with the current gradient; the right Gram reuses the pulled panel X[:, my row class]
+        with TIMER.stage("gram", device):
+            _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
+            _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right", gathered=x_panel)
+            _mirror_upper(e, [("left", state["left_preconditioner"], rows), ("right", state["right_preconditioner"], cols)],
+                          channel=channel)
+            e.comm.barrier(channel=channel)
+
+    # The Gram updates depend on the gradient only.  They run on a stream of their own (with their own barrier
+    # channel) beside the rotations, so that their products fill the SMs while the rotations wait for pulls and
+    # barriers and vice versa.
+    gram_done = None
+    if OVERLAP_GRAM:
+        side = e.side_stream()
+        pulled = torch.cuda.Event()
+        pulled.record(main)
+        side.wait_event(pulled)
+        with torch.cuda.stream(side):
+            gram_updates(channel=1)
+            gram_done = torch.cuda.Event()
+            gram_done.record(side)
     # forward rotation straight from the tensor-parallel shards, Adam in the epilogue, update -> segment
     with TIMER.stage("rotate_forward+adam", device):
         _, u_view, u_source = e.packed_segment("update", global_shape)
-        x_panel = e.planes("x_panel", rows, e.rows_of(cols))   # X[:, my row class]; reused by the right Gram
-        e.two_sided(shard_source, global_shape, left_plain, right_plain, panel=x_panel, mode=k.EPI_ADAM,
+        e.two_sided(shard_source, global_shape, left_plain, right_plain, panel=x_panel, gathered=True, mode=k.EPI_ADAM,
                     out=u_view[: max(1, lr), : max(1, lc)],
                     momentum=state["momentum"][: max(1, lr), : max(1, lc)],
                     variance=state["variance"][: max(1, lr), : max(1, lc)], adam=adam)
@@ -753,12 +787,10 @@ def soap_step(gradient_shard: Tensor, state: MutableMapping[str, Any], *, global
         e.two_sided(u_source, global_shape, left_t, right_t, mode=k.EPI_STORE, out=o_view[: max(1, lr), : max(1, lc)])
         e.comm.barrier()
         update = _pull_shard(e, o_source, global_shape, shard_dim)
-    # Gram EMAs with the current gradient; the right Gram reuses the gathered panel X[:, my row class]
-    with TIMER.stage("gram", device):
-        _gram_from_source(e, shard_source, global_shape, state["left_preconditioner"], beta, "left")
-        _gram_from_source(e, shard_source, global_shape, state["right_preconditioner"], beta, "right", gathered=x_panel)
-        _mirror_upper(e, [("left", state["left_preconditioner"], rows), ("right", state["right_preconditioner"], cols)])
-        e.comm.barrier()
+    if gram_done is not None:
+        main.wait_event(gram_done)
+    else:
+        gram_updates(channel=0)
     if step % interval == 0:
         with TIMER.stage("refresh", device):
             refresh(e, state, global_shape)

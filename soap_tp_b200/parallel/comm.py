@@ -61,6 +61,8 @@ def default_barrier_timeout() -> float:
 
 
 class Communicator:
+    CHANNELS = 4     # independent barrier channels: barriers issued on different streams use different channels
+
     def __init__(self, device: torch.device, *, group=None, barrier_timeout_s: Optional[float] = None) -> None:
         """``group``: the process group whose ranks form the grid (default: the world).  Every rank of the group
         must construct its communicator at the same point of the program."""
@@ -87,7 +89,6 @@ class Communicator:
             self.control = group
         self.control_on_device = "gloo" not in str(dist.get_backend(self.control))
         self.segments: Dict[str, SymmetricSegment] = {}
-        self._epoch = 0
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         identity = (os.uname().nodename, bytes(self._C.device_uuid(index)))
         everyone: List[Optional[tuple]] = [None] * self.world
@@ -96,7 +97,9 @@ class Communicator:
         if len({host for host, _ in everyone}) != 1:
             raise RuntimeError("the CUDA IPC communicator needs all ranks on one node.")
         self.use_device_barrier = self.exclusive_gpus and os.environ.get("SOAP_TP_HOST_BARRIER", "0") != "1"
-        self._pads = self.segment("signal_pads", max(self.world, 64), torch.int32) if self.world > 1 else None
+        self._channel_stride = max(self.world, 64)
+        self._pads = self.segment("signal_pads", self.CHANNELS * self._channel_stride, torch.int32) if self.world > 1 else None
+        self._epochs = [0] * self.CHANNELS
         self.barrier_count = 0
 
     # ---- symmetric segments ------------------------------------------------------------------
@@ -127,9 +130,12 @@ class Communicator:
         return seg
 
     # ---- ordering ----------------------------------------------------------------------------
-    def barrier(self, *, after_long_work: bool = False) -> None:
+    def barrier(self, *, after_long_work: bool = False, channel: int = 0) -> None:
         """All work enqueued so far on every rank's current stream happens-before anything
         enqueued after this call on any rank.
+
+        ``channel``: barriers that run on different streams at the same time must use different channels (each has
+        its own flags and epoch counter); every rank issues the barriers of a channel in the same order.
 
         ``after_long_work``: some rank has just enqueued work that may take longer than the device barrier's
         spin budget (a dense factorisation on a leader rank).  Every rank then first drains its own stream and
@@ -145,10 +151,10 @@ class Communicator:
         if self.use_device_barrier:
             from ..engine import kernels
 
-            self._epoch += 1
-            self._C.device_barrier(self._pads.peer_table.data_ptr(), self.rank, self.world, self._epoch,
+            self._epochs[channel] += 1
+            self._C.device_barrier(self._pads.peer_table.data_ptr(), self.rank, self.world, self._epochs[channel],
                                    kernels.status_word(self.device).data_ptr(), float(self.barrier_timeout_s),
-                                   torch.cuda.current_stream().cuda_stream)
+                                   torch.cuda.current_stream().cuda_stream, channel * self._channel_stride)
             kernels._count("barrier_kernel")
         else:
             torch.cuda.current_stream().synchronize()

@@ -125,7 +125,8 @@ def _long_leader_work_is_awaited_on_the_host(rank, world):
     class Recorder(comm_module.Communicator):
         def __init__(self):            # no device, no segments: only the ordering logic is under test
             self.world, self.rank, self.control = world, rank, dist.group.WORLD
-            self.use_device_barrier, self.barrier_count, self._epoch = True, 0, 0
+            self.use_device_barrier, self.barrier_count = True, 0
+            self._epochs, self._channel_stride = [0] * self.CHANNELS, 64
             self.device, self.barrier_timeout_s = torch.device("cpu"), 0.2
             self.arrivals = []
 
