@@ -102,7 +102,7 @@ def gram_error(state: MutableMapping, gradients: Callable[[int], Tensor], histor
 
 def side_problem_against_one_gpu(step_fn_factory: Callable[[], Callable[[Tensor], Tensor]], size: int, block: int, grid,
                                  shard_dim: int, steps: int, interval: int, scale: float = 1e-2,
-                                 implementation: str = "householder") -> Dict[str, float]:
+                                 implementation: str = "householder", state: MutableMapping = None) -> Dict[str, float]:
     """Run ``steps`` calls on a ``size x size`` parameter through the distributed path (``step_fn_factory()``
     returns a fresh ``step(shard) -> update shard``) and, on every rank, through the single-GPU pipeline with
     the full gradient; report the worst relative L2 distance of the updates and the step it occurred at."""
@@ -116,6 +116,7 @@ def side_problem_against_one_gpu(step_fn_factory: Callable[[], Callable[[Tensor]
     shape = (size, size)
     single: dict = {}
     worst, worst_step = 0.0, -1
+    per_step: List[float] = []
     generator = torch.Generator(device=device)
     for index in range(steps):
         generator.manual_seed(77_000 + index)
@@ -134,6 +135,19 @@ def side_problem_against_one_gpu(step_fn_factory: Callable[[], Callable[[Tensor]
         if index == 0:
             continue
         distance = float((gathered - expected).norm() / expected.norm())
+        per_step.append(distance)
         if distance > worst:
             worst, worst_step = distance, index
-    return {"worst_relative_l2": worst, "at_step": worst_step, "steps": steps, "size": size}
+    result = {"worst_relative_l2": worst, "at_step": worst_step, "steps": steps, "size": size,
+              "per_step": [float(f"{d:.3e}") for d in per_step]}
+    if state is not None:
+        # the preconditioners are rounding-level functions of the gradients; the bases after a refresh carry the
+        # conditioning of the QR factor (a perturbation of relative size eps moves Q by about eps * cond(P Q))
+        for name in ("left_preconditioner", "right_preconditioner", "left_basis"):
+            dense = gather_dense(state[name], shape, block, grid)
+            reference = single[name][:size, :size]
+            if name == "left_basis":
+                signs = torch.sign((dense * reference).sum(dim=0))
+                dense = dense * torch.where(signs == 0, torch.ones_like(signs), signs)
+            result[name + "_relative_difference"] = float((dense - reference).norm() / reference.norm())
+    return result

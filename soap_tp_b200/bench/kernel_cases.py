@@ -7,6 +7,7 @@
     python -m soap_tp_b200.bench.kernel_cases update --size 4096      # QR trailing update (K = 128, planes RMW)
     python -m soap_tp_b200.bench.kernel_cases adam --size 8192
     python -m soap_tp_b200.bench.kernel_cases split --size 8192
+    python -m soap_tp_b200.bench.kernel_cases eig --size 4096 [--solver householder|jacobi]
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m soap_tp_b200.bench.kernel_cases \
         gather --size 8192                                          # peer pull, traffic mix of an 8-GPU (2, 4) grid
 
@@ -105,7 +106,8 @@ def gather_case(args) -> int:
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("case", choices=("gemm", "qr", "qrpair", "panel", "update", "adam", "split", "gather"))
+    parser.add_argument("case", choices=("gemm", "qr", "qrpair", "panel", "update", "adam", "split", "gather", "eig"))
+    parser.add_argument("--solver", choices=("householder", "jacobi"), default="householder", help="eig: which eigensolver")
     parser.add_argument("--size", type=int, default=4096)
     parser.add_argument("--rows", type=int, default=4096)
     parser.add_argument("--mode", default="store")
@@ -199,6 +201,16 @@ def main(argv=None) -> int:
             us = timed(fn, args.repeats)
             print(f"trailing update {n} x {n - 128}, K=128: {us:.1f} us/launch, "
                   f"{n * (n - 128) * 16 / us / 1e6:.2f} TB/s of plane traffic")
+    elif args.case == "eig":
+        from ..engine import jacobi, tridiag
+
+        G = rand(n, n) * 1e-2
+        P = (0.05 * (G.double() @ G.double().T)).float().T.contiguous().T      # a Gram matrix, as at initialisation
+        Q, values, work = torch.empty(n, n, device=device).T, torch.empty(n, device=device), torch.empty(n, n, device=device).T
+        solver = tridiag if args.solver == "householder" else jacobi
+        us = timed(lambda: solver.symmetric_eigenbasis(P, Q, work, values), max(1, args.repeats - 2))
+        residual = float((P @ Q - Q * values).abs().max() / values.abs().max())
+        print(f"symmetric eigensolver ({args.solver}) {n}: {us / 1e3:.1f} ms, largest |P Q - Q diag| / largest eigenvalue {residual:.2e}")
     elif args.case == "adam":
         g, m, v = (torch.rand(n, n, device=device).T for _ in range(3))
         us = timed(lambda: k.adam_update(g, m, v, 0.9, 0.99, 1e-8, 0.5, 0.5), args.repeats)

@@ -16,8 +16,10 @@ import argparse
 import os
 import time
 
-import torch
-import torch.distributed as dist
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")    # no lazy kernel loading in the middle of a training step
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
 
 from .models.llama_tp import LlamaConfig, LlamaTP
 from .optim import SoapTP
