@@ -46,7 +46,7 @@ def step(gradient: Tensor, state: MutableMapping[str, Any], *, beta: float, beta
         fresh = local.workspace_matrix("os_gram", h, h, device)
         k.gemm(gp, gp, out=fresh, symmetric=True)                      # G_r^T G_r
         if world > 1:
-            dist.all_reduce(fresh)
+            dist.all_reduce(fresh.T)               # the contiguous view of the column-major buffer (same layout on every rank)
         state["right_preconditioner"].mul_(beta).add_(fresh, alpha=1.0 - beta)
 
     if "right_basis" not in state:

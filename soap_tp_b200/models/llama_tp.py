@@ -22,6 +22,7 @@ from dataclasses import dataclass
 from typing import Optional
 
 import torch
+import torch.utils.checkpoint
 import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
@@ -264,6 +265,9 @@ class LlamaTP(nn.Module):
         self.final_norm = RMSNorm(cfg.hidden_size, cfg.rms_eps, dtype=dtype, device=device)
         self.lm_head = ColumnParallelLinear(cfg.hidden_size, cfg.vocab_size, dtype=dtype, device=device, std=std)
         self.vocab_start = _rank() * (cfg.vocab_size // _world())
+        # recompute every block in the backward pass instead of keeping its activations (32 layers at sequence
+        # length 4096 and batch 8 would otherwise hold over 100 GB of activations per rank)
+        self.checkpoint_activations = False
 
     def forward(self, tokens: Tensor, targets: Optional[Tensor] = None) -> Tensor:
         """Mean next-token loss if ``targets`` is given, else this rank's slice of the logits."""
@@ -271,7 +275,10 @@ class LlamaTP(nn.Module):
         cos, sin = rope_tables(self.cfg.hidden_size // self.cfg.num_heads, seq, self.cfg.rope_theta, tokens.device)
         x = self.embed(tokens)
         for block in self.blocks:
-            x = block(x, cos, sin)
+            if self.checkpoint_activations and torch.is_grad_enabled():
+                x = torch.utils.checkpoint.checkpoint(block, x, cos, sin, use_reentrant=False)
+            else:
+                x = block(x, cos, sin)
         logits = self.lm_head(self.final_norm(x))
         if targets is None:
             return logits

@@ -4,9 +4,9 @@
         --preset llama3-8b --seq-len 4096 --global-batch 8 --steps 5
 
 One process per GPU (NCCL); ``--device cpu`` runs the same code on gloo ranks with the tiny preset.
-SOAP-TP runs on every 2-D tensor-parallel weight whose sides do not exceed ``--max-precond-dim``
-(the vocabulary-sized matrices of the 8B preset fall back to AdamW: a two-sided preconditioner of a
-128256 x 128256 Gram matrix is 61 GiB per buffer), AdamW on 1-D parameters.  Token ids are uniform
+SOAP-TP runs on every 2-D tensor-parallel weight: two-sided where both sides are at most ``--max-precond-dim``,
+one-sided (identity basis on the sharded, vocabulary-sized side, as original SOAP does above its
+``max_precond_dim``) for the embedding and the head; AdamW on 1-D parameters.  Token ids are uniform
 random (there is no dataset here); weights are random-initialised in bf16, optimizer state is fp32.
 Rank 0 prints one ``SOAP_TIMING``-style JSON line per step and a summary.
 """
@@ -40,6 +40,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--basis-implementation", default="householder")
     parser.add_argument("--device", choices=("cuda", "cpu"), default="cuda")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--checkpoint-activations", action="store_true",
+                        help="recompute each decoder block in the backward pass (needed for all 32 layers of the 8B preset)")
     return parser.parse_args(argv)
 
 
@@ -62,6 +64,7 @@ def train(args: argparse.Namespace) -> dict:
     seq_len = args.seq_len or cfg.max_seq_len
     dtype = torch.bfloat16 if args.device == "cuda" else torch.float32
     model = LlamaTP(cfg, dtype=dtype, device=device, seed=args.seed)
+    model.checkpoint_activations = bool(args.checkpoint_activations)
     matrices, others = model.soap_parameters()
     optimizer = SoapTP(
         [{"params": matrices}, {"params": others, "weight_decay": 0.0}],
@@ -92,8 +95,11 @@ def train(args: argparse.Namespace) -> dict:
         emit_timing("step", step=step, seconds=seconds[-1], loss=losses[-1],
                     tokens_per_second=args.global_batch * seq_len / seconds[-1])
     summary = dict(losses=losses, seconds=seconds)
+    peak = torch.cuda.max_memory_allocated(device) / 2**30 if device.type == "cuda" else None
     emit_timing("summary", ranks=world, measured_steps=args.steps, seconds_per_step=sum(seconds) / max(1, len(seconds)),
-                final_loss=losses[-1] if losses else None)
+                final_loss=losses[-1] if losses else None, peak_allocated_gib=peak,
+                one_sided_parameters=sum(1 for g in optimizer.param_groups for p in g["params"]
+                                         if (optimizer._plan(p, g) or {}).get("one_sided")))
     if created:
         dist.destroy_process_group()
     return summary
