@@ -113,6 +113,11 @@ PYBIND11_MODULE(_C, m) {
           column_dot(ptr<const float>(a), lda, ptr<const float>(b), ldb, ptr<float>(out), rows, cols, stream_of(stream));
         });
 
+  m.def("order_by_estimate", [](uint64_t table, int64_t ld, int parts, int n, uint64_t order, uint64_t stream) {
+    order_by_estimate(ptr<const float>(table), ld, parts, n, ptr<int64_t>(order), stream_of(stream));
+  });
+  m.attr("ORDER_MAX_LENGTH") = kOrderMaxLength;
+
   m.def("gather2d",
         [](uint64_t src, int64_t s_i, int64_t s_j, uint64_t dst, int64_t d_i, int64_t d_j, uint64_t row_map,
            uint64_t col_map, int rows, int cols, uint64_t stream) {

@@ -7,6 +7,7 @@
 
 #include "elementwise.h"
 #include "gemm.h"
+#include "launch_util.h"
 
 namespace soapb200 {
 namespace {
@@ -128,6 +129,48 @@ __global__ void __launch_bounds__(256) column_dot_kernel(const float* __restrict
   if (threadIdx.x == 0) out[j] = partial[0];
 }
 
+// ---- stable descending order of column sums ------------------------------------------------------
+// estimates[j] = sum_r table[r + j * ld] (r < parts, fixed order); order = indices sorted by descending estimate, ties by
+// ascending index (what a stable descending argsort returns).  One CTA, bitonic sort of (value, index) pairs in shared
+// memory; `padded` is the power of two >= n that the launch was sized for.
+__global__ void __launch_bounds__(1024) order_by_estimate_kernel(const float* __restrict__ table, int64_t ld, int parts,
+                                                                 int n, int padded, int64_t* __restrict__ order) {
+  extern __shared__ unsigned char sort_raw[];
+  float* keys = reinterpret_cast<float*>(sort_raw);
+  int* index = reinterpret_cast<int*>(keys + padded);
+  for (int j = threadIdx.x; j < padded; j += blockDim.x) {
+    float total = -INFINITY;                       // padding sorts to the end
+    if (j < n) {
+      total = 0.f;
+      for (int r = 0; r < parts; ++r) total += table[r + j * ld];
+      if (total != total) total = -INFINITY;       // a NaN estimate goes last instead of poisoning the network
+    }
+    keys[j] = total;
+    index[j] = j;
+  }
+  __syncthreads();
+  // "a precedes b" in the wanted order: larger value first, smaller index first among equals
+  auto precedes = [](float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); };
+  for (int size = 2; size <= padded; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < padded / 2; t += blockDim.x) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool ascending_block = (lo & size) == 0;        // blocks alternate direction
+        const float va = keys[lo], vb = keys[hi];
+        const int ia = index[lo], ib = index[hi];
+        const bool in_order = precedes(va, ia, vb, ib);
+        if (in_order != ascending_block) {
+          keys[lo] = vb; keys[hi] = va;
+          index[lo] = ib; index[hi] = ia;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int j = threadIdx.x; j < n; j += blockDim.x) order[j] = index[j];
+}
+
 // ---- gather: dst(i, j) = src(row_map[i], col_map[j]) with null maps meaning identity ----------
 __global__ void gather2d_kernel(const float* __restrict__ src, int64_t s_i, int64_t s_j, float* __restrict__ dst,
                                 int64_t d_i, int64_t d_j, const int64_t* __restrict__ row_map,
@@ -184,6 +227,18 @@ void column_dot(const float* a, int64_t lda, const float* b, int64_t ldb, float*
   if (cols <= 0) return;
   column_dot_kernel<<<cols, 256, 0, stream>>>(a, lda, b, ldb, out, rows, cols);
   check_launch("column_dot_kernel");
+}
+
+void order_by_estimate(const float* table, int64_t ld, int parts, int n, int64_t* order, cudaStream_t stream) {
+  if (n <= 0) return;
+  int padded = 1;
+  while (padded < n) padded <<= 1;
+  if (padded > kOrderMaxLength) throw std::invalid_argument("order_by_estimate: more entries than one CTA's shared memory sorts");
+  const size_t smem = static_cast<size_t>(padded) * (sizeof(float) + sizeof(int));
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(order_by_estimate_kernel), kOrderMaxLength * 8, configured, "order_by_estimate");
+  order_by_estimate_kernel<<<1, 1024, smem, stream>>>(table, ld, parts, n, padded, order);
+  check_launch("order_by_estimate_kernel");
 }
 
 void gather2d(const float* src, int64_t s_i, int64_t s_j, float* dst, int64_t d_i, int64_t d_j, const int64_t* row_map,

@@ -20,6 +20,11 @@ void split_planes(const float* src, int64_t s_i, int64_t s_j, float* hi, float* 
 void column_dot(const float* a, int64_t lda, const float* b, int64_t ldb, float* out, int rows, int cols,
                 cudaStream_t stream);
 
+// order = stable descending argsort of estimates[j] = sum_{r < parts} table[r + j * ld], j < n <= kOrderMaxLength
+// (one CTA, shared-memory bitonic sort; NaN estimates sort last).
+constexpr int kOrderMaxLength = 16384;
+void order_by_estimate(const float* table, int64_t ld, int parts, int n, int64_t* order, cudaStream_t stream);
+
 // dst(i, j) = src(row_map[i], col_map[j]); a null map is the identity.
 void gather2d(const float* src, int64_t s_i, int64_t s_j, float* dst, int64_t d_i, int64_t d_j, const int64_t* row_map,
               const int64_t* col_map, int rows, int cols, cudaStream_t stream);

@@ -552,8 +552,7 @@ def estimated_order(P: Tensor, Q: Tensor, work: Tensor, size: int, block_size: i
         dist_gather(source, IDENTITY, IDENTITY, e.Pr, size, out=table)
         e.comm.barrier()
     with TIMER.stage("refresh.power_iteration.sort", P.device):
-        estimates = table.sum(dim=0)   # fixed order over Pr -> identical on every rank
-        order = torch.argsort(estimates, descending=True, stable=True)
+        order = k.order_by_estimate(table)   # column sums in fixed order over Pr -> identical on every rank
     return order
 
 

@@ -388,6 +388,20 @@ def column_dot(a: Tensor, b: Tensor, rows: int, cols: int, out: Optional[Tensor]
     return out
 
 
+def order_by_estimate(table: Tensor) -> Tensor:
+    """Stable descending order of the column sums of ``table`` (``parts x n``, any strides with unit row stride or a
+    single row): the eigenvalue order of a refresh.  One launch of this library's sort kernel for ``n`` up to
+    ``ORDER_MAX_LENGTH``; longer vectors use the framework's sort."""
+    parts, n = table.shape
+    if n > _C.ORDER_MAX_LENGTH or (parts > 1 and table.stride(0) != 1):
+        return torch.argsort(table.sum(dim=0), descending=True, stable=True)
+    order = torch.empty(n, dtype=torch.int64, device=table.device)
+    ld = table.stride(1) if n > 1 else parts
+    _C.order_by_estimate(table.data_ptr(), ld, parts, n, order.data_ptr(), _stream())
+    _count("order_by_estimate_kernel")
+    return order
+
+
 def gather2d(src: Tensor, dst: Tensor, row_map: Optional[Tensor], col_map: Optional[Tensor]) -> Tensor:
     """``dst[i, j] = src[row_map[i], col_map[j]]`` (``None`` = identity); ``dst`` must not alias ``src``."""
     rows, cols = dst.shape

@@ -187,14 +187,13 @@ def warm_refresh_kernels(device, sizes=()) -> None:
     """Launch every kernel variant a refresh uses once, on a tiny problem.
 
     CUDA loads a kernel's code the first time it is launched; without this the first refresh of a
-    training run pays tens of milliseconds of module loading in the middle of a step.  The library sort
-    picks its kernels by length, so the eigenvalue-order sort is warmed at the real ``sizes``.
+    training run pays tens of milliseconds of module loading in the middle of a step.  The eigenvalue-order sort
+    sizes its shared memory by length, so it is warmed at the real ``sizes``.
     """
     for size in sizes:
         if not _WARMED.get((str(torch.device(device)), "sort", size)):
             _WARMED[(str(torch.device(device)), "sort", size)] = True
-            table = torch.rand((size, 2), device=device).T
-            torch.argsort(table.sum(dim=0), descending=True, stable=True)
+            k.order_by_estimate(torch.rand((size, 2), device=device).T)
     key = str(torch.device(device))
     if _WARMED.get(key):
         return
@@ -255,7 +254,7 @@ def estimated_order(P: Tensor, Q: Tensor, work: Tensor, size: int) -> Tensor:
     qp = k.split_planes(Q[:size, :size], out=workspace_planes("Qtmp", size, size, device))
     k.gemm(pp, qp, out=work[:size, :size])
     estimates = k.column_dot(Q, work, size, size)
-    return torch.argsort(estimates, descending=True, stable=True)
+    return k.order_by_estimate(estimates.view(1, size))
 
 
 def power_iteration_qr(P: Tensor, Q: Tensor, work: Tensor, size: int) -> Tensor:
@@ -269,7 +268,7 @@ def permute(matrix: Tensor, global_shape, row_order: Tensor, column_order: Tenso
     scratch = workspace_matrix("perm", rows, cols, matrix.device)
     view = matrix[:rows, :cols]
     k.gather2d(view, scratch, row_order, column_order)
-    view.copy_(scratch)
+    k.gather2d(scratch, view, None, None)
     return matrix
 
 
