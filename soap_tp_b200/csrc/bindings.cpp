@@ -84,6 +84,9 @@ PYBIND11_MODULE(_C, m) {
       py::arg("ldp16") = 0,
       "3xTF32 tcgen05 GEMM acc[m,n] = sum_k Za[k,m] Zb[k,n] with fused epilogue");
 
+  m.def("gemm_use_cta_pairs", [](bool on) { gemm_use_cta_pairs(on); },
+        "Large plain GEMMs on CTA pairs (cta_group::2, default) or on single CTAs");
+
   m.def("gemm_simt",
         [](uint64_t A, int64_t a_sk, int64_t a_sm, uint64_t B, int64_t b_sk, int64_t b_sn, uint64_t C, int64_t c_sm,
            int64_t c_sn, int M, int N, int K, float alpha, float beta, uint64_t stream) {

@@ -78,6 +78,9 @@ struct GemmProblem {
 // `status` is the device status word that bounded waits report to.
 void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream);
 
+// Large plain problems run on CTA pairs (cta_group::2) by default; `false` keeps every launch on single CTAs.
+void gemm_use_cta_pairs(bool on);
+
 // Same contraction in plain fp32 FMA on CUDA cores from unsplit operands with arbitrary strides:
 // acc[m, n] = sum_k A[k*a_sk + m*a_sm] * B[k*b_sk + n*b_sn];  C[m*c_sm + n*c_sn] = alpha*acc + beta*C.
 // Used as the in-tree numerical cross-check of the tensor-core kernel and for problems far below one tile.

@@ -580,6 +580,211 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same product on CTA pairs (`cta_group::2`): the two CTAs of a cluster compute a 256 x 256 tile together.  Each CTA
+// stages its own 128 rows of A and HALF of the 256 rows of B (each with its own TMA, no multicast), the leader CTA issues
+// M = 256 MMAs that read both CTAs' shared memory, and each CTA's TMEM receives its own 128 x 256 half of the
+// accumulator, which it promotes and stores exactly as the single-CTA kernel does.  Per k-block a CTA therefore loads
+// 64 KB instead of 96 KB: operand traffic from L2 into shared memory, which is what bounds the single-CTA kernel once the
+// correction products run as bf16 MMAs, drops by a third, and three stages fit instead of two.
+constexpr int kPairStages = 3;
+constexpr int kPairStageBytes = 2 * (kBM + 128) * kBK * 4;       // A (hi, second plane) + half of B (hi, second plane)
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr int kPairBN = 256;
+
+template <int MODE, bool MIXED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmProblem prob, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);   // used in the leader CTA only
+  uint64_t* empty_bar = full_bar + kPairStages;      // each CTA its own: "my stage may be refilled"
+  uint64_t* acc_full = empty_bar + kPairStages;      // [2] each CTA its own: tensor core -> epilogue
+  uint64_t* acc_empty = acc_full + 2;                // [2] leader's only: epilogue warps of BOTH CTAs -> tensor core
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_cta_rank();           // 0: leader (issues the MMAs), 1: peer
+  constexpr int BN = kPairBN;
+
+  // Grouped raster over pair tiles: 8 pair-rows share their B panels in L2 while they sweep the tile columns.
+  const int tiles_m = (prob.M + 2 * kBM - 1) / (2 * kBM);
+  const int tiles_n = (prob.N + BN - 1) / BN;
+  constexpr int kGroup = 8;
+  int tile_m, tile_n;
+  {
+    const int pair = blockIdx.x >> 1;
+    const int per_group = kGroup * tiles_n;
+    const int group = pair / per_group;
+    const int first_m = group * kGroup;
+    const int rows_in_group = min(kGroup, tiles_m - first_m);
+    const int within = pair % per_group;
+    tile_m = first_m + within % rows_in_group;
+    tile_n = within / rows_in_group;
+  }
+  const int pair_m0 = tile_m * 2 * kBM;
+  const int m0 = pair_m0 + static_cast<int>(cta) * kBM;      // this CTA's rows of the result
+  const int n0 = tile_n * BN;
+  const int b_row0 = n0 + static_cast<int>(cta) * (BN / 2);  // this CTA's half of the B tile
+  // Symmetric products: pair tiles strictly above the diagonal are produced by mirroring (same decision in both CTAs).
+  if (prob.symmetric && global_col(prob, n0) > global_row(prob, min(pair_m0 + 2 * kBM, prob.M) - 1)) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 2 * kEpiWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_descriptor(&maps.a_hi);
+    tma_prefetch_descriptor(&maps.a_lo);
+    tma_prefetch_descriptor(&maps.b_hi);
+    tma_prefetch_descriptor(&maps.b_lo);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 2 * BN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                 // both CTAs' barriers exist before anything arrives on them remotely
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int k_blocks = (prob.K + kBK - 1) / kBK;
+  const int chunks = (k_blocks + kPromote - 1) / kPromote;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer (each CTA loads its own tiles; the bytes are credited to the leader's barrier) ----------------
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      const int s = kb % kPairStages;
+      const uint32_t round = kb / kPairStages;
+      if (kb >= kPairStages &&
+          !mbar_wait_bounded(&empty_bar[s], (round - 1) & 1, abort_flag, status, kStatusSlotWaitTimeout))
+        break;
+      uint8_t* stage = smem + s * kPairStageBytes;
+      if (cta == 0) mbar_expect_tx(&full_bar[s], 2 * kPairStageBytes);
+      const uint32_t leader_bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+      const int k0 = kb * kBK;
+      const int k2 = MIXED ? 2 * k0 : k0;        // the interleaved bf16 plane has 64 elements per 32 of K
+      tma_load_2d_pair(stage, &maps.a_hi, leader_bar, k0, m0);
+      tma_load_2d_pair(stage + kBM * kRowBytes, &maps.a_lo, leader_bar, k2, m0);
+      tma_load_2d_pair(stage + 2 * kBM * kRowBytes, &maps.b_hi, leader_bar, k0, b_row0);
+      tma_load_2d_pair(stage + 2 * kBM * kRowBytes + (BN / 2) * kRowBytes, &maps.b_lo, leader_bar, k2, b_row0);
+    }
+    if (*abort_flag) {
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1 && lane == 0 && cta == 0) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    constexpr uint32_t idesc = umma_idesc_tf32(2 * kBM, BN);
+    constexpr uint32_t idesc16 = umma_idesc_bf16(2 * kBM, BN);
+    bool ok = true;
+    int kb = 0;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int buf = c & 1;
+      if (c >= 2) {
+        ok = mbar_wait_bounded(&acc_empty[buf], ((c >> 1) - 1) & 1, abort_flag, status, kStatusAccumWaitTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(buf * BN);
+      const int kb_end = min(k_blocks, kb + kPromote);
+      for (int first = 1; kb < kb_end; ++kb) {
+        const int s = kb % kPairStages;
+        const uint32_t round = kb / kPairStages;
+        ok = mbar_wait_bounded(&full_bar[s], round & 1, abort_flag, status, kStatusTmaWaitTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t stage = smem_u32(smem + s * kPairStageBytes);
+        const uint64_t a_hi = umma_desc_kmajor<kRowBytes>(stage);
+        const uint64_t a_2 = umma_desc_kmajor<kRowBytes>(stage + kBM * kRowBytes);
+        const uint64_t b_hi = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes);
+        const uint64_t b_2 = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes + (BN / 2) * kRowBytes);
+        if constexpr (MIXED) {
+          constexpr uint64_t kLb = 64 >> 4;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+            umma_bf16_ss_pair(tmem_acc, a_2 + kLb + adv, b_2 + adv, idesc16, first ? 0u : 1u);     // lo * hi
+            first = 0;
+            umma_bf16_ss_pair(tmem_acc, a_2 + adv, b_2 + kLb + adv, idesc16, 1);                   // hi * lo
+          }
+#pragma unroll
+          for (int k = 0; k < kBK / 8; ++k) {
+            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+            umma_tf32_ss_pair(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < kBK / 8; ++k) {
+            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+            umma_tf32_ss_pair(tmem_acc, a_2 + adv, b_hi + adv, idesc, first ? 0u : 1u);
+            first = 0;
+            umma_tf32_ss_pair(tmem_acc, a_hi + adv, b_2 + adv, idesc, 1);
+            umma_tf32_ss_pair(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+          }
+        }
+        umma_commit_pair(&empty_bar[s]);  // both CTAs' stage s may be refilled once these UMMAs have read it
+      }
+      if (ok) umma_commit_pair(&acc_full[buf]);
+    }
+  } else if (warp >= 2) {
+    // ---------------- promotion + epilogue (each CTA its own 128 rows) ----------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int half = ew >> 2;
+    constexpr int kCols = BN / 2;
+    const int col0 = half * kCols;
+    const uint32_t leader_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+    float sum[kCols];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) sum[j] = 0.0f;
+    bool ok = true;
+    for (int c = 0; c < chunks && ok; ++c) {
+      const int buf = c & 1;
+      ok = mbar_wait_bounded(&acc_full[buf], (c >> 1) & 1, abort_flag, status, kStatusAccumWaitTimeout);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(buf * BN + col0);
+#pragma unroll
+      for (int cc = 0; cc < kCols; cc += 32) {
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + static_cast<uint32_t>(cc), raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[cc + j] += __uint_as_float(raw[j]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + static_cast<uint32_t>(buf * sizeof(uint64_t)));
+    }
+    float* tile = reinterpret_cast<float*>(smem);
+    {
+      const int m_local = quarter * 32 + lane;
+#pragma unroll
+      for (int jx = 0; jx < kCols; ++jx) tile[(col0 + jx) * kTilePitch + m_local] = sum[jx];
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kEpiWarps * 32) : "memory");
+    if (ok && m0 < prob.M) run_epilogue<BN, MODE>(prob, tile, m0, n0, ew, lane, 0);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                 // nobody leaves while the other CTA may still touch its shared memory or TMEM
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 2 * BN);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side: tensor maps (driver entry point fetched at run time, so no link-time libcuda) and launch.
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -660,7 +865,35 @@ void launch(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaS
   if (err != cudaSuccess) throw std::runtime_error(std::string("gemm_tf32x3 launch: ") + cudaGetErrorString(err));
 }
 
+template <int MODE, bool MIXED>
+void launch_pair(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
+  static PerDeviceOnce configured;
+  allow_dynamic_smem(reinterpret_cast<const void*>(gemm_pair_kernel<MODE, MIXED>), kPairSmemBytes, configured, "gemm_pair");
+  GemmMaps maps;
+  const int64_t a_k = ops.a_k_total ? ops.a_k_total : prob.K, a_rows = ops.a_rows_total ? ops.a_rows_total : prob.M;
+  const int64_t b_k = ops.b_k_total ? ops.b_k_total : prob.K, b_rows = ops.b_rows_total ? ops.b_rows_total : prob.N;
+  maps.a_hi = make_operand_map(ops.a_hi, a_k, a_rows, ops.lda, kBM);
+  maps.b_hi = make_operand_map(ops.b_hi, b_k, b_rows, ops.ldb, kPairBN / 2);
+  if constexpr (MIXED) {
+    maps.a_lo = make_bf16_map(ops.a_hl, a_k, a_rows, ops.lda16, kBM);
+    maps.b_lo = make_bf16_map(ops.b_hl, b_k, b_rows, ops.ldb16, kPairBN / 2);
+  } else {
+    maps.a_lo = make_operand_map(ops.a_lo, a_k, a_rows, ops.lda, kBM);
+    maps.b_lo = make_operand_map(ops.b_lo, b_k, b_rows, ops.ldb, kPairBN / 2);
+  }
+  const int tiles_m = (prob.M + 2 * kBM - 1) / (2 * kBM);
+  const int tiles_n = (prob.N + kPairBN - 1) / kPairBN;
+  dim3 grid(2 * tiles_m * tiles_n, 1, 1);
+  gemm_pair_kernel<MODE, MIXED><<<grid, kThreads, kPairSmemBytes, stream>>>(maps, prob, status);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) throw std::runtime_error(std::string("gemm_pair launch: ") + cudaGetErrorString(err));
+}
+
+bool g_use_pairs = true;
+
 }  // namespace
+
+void gemm_use_cta_pairs(bool on) { g_use_pairs = on; }
 
 void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
   if (prob.M <= 0 || prob.N <= 0) return;
@@ -678,6 +911,23 @@ void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, 
       wide ? launch<256, MODE_, false>(ops, prob, status, stream) : launch<128, MODE_, false>(ops, prob, status, stream); \
     }                                                                                                \
   } while (0)
+  // CTA pairs for large plain problems: no batching, no split-K
+  const bool pairs = g_use_pairs && wide && kBK == 32 && prob.M >= 2 * kBM && prob.batches <= 1 && prob.k_splits <= 1 &&
+                     prob.mode != kEpiPairUpdate;
+  if (pairs) {
+#define SOAP_PAIR_LAUNCH(MODE_)                                                                                  \
+  do {                                                                                                           \
+    if (mixed) launch_pair<MODE_, true>(ops, prob, status, stream); else launch_pair<MODE_, false>(ops, prob, status, stream); \
+  } while (0)
+    switch (prob.mode) {
+      case kEpiStore: SOAP_PAIR_LAUNCH(kEpiStore); return;
+      case kEpiSplit: SOAP_PAIR_LAUNCH(kEpiSplit); return;
+      case kEpiAdam: SOAP_PAIR_LAUNCH(kEpiAdam); return;
+      case kEpiRowMajor: SOAP_PAIR_LAUNCH(kEpiRowMajor); return;
+      default: break;
+    }
+#undef SOAP_PAIR_LAUNCH
+  }
   switch (prob.mode) {
     case kEpiStore:
       SOAP_GEMM_LAUNCH(kEpiStore);

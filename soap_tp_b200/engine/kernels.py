@@ -152,6 +152,17 @@ def round_up(value: int, multiple: int) -> int:
 MIXED_CORRECTIONS = os.environ.get("SOAP_TP_MIXED_CORRECTIONS", "1") != "0"
 
 
+def use_cta_pairs(on: bool) -> None:
+    """Large plain products (at least 148 tiles of 128 x 256, no batching, no split-K) run on CTA pairs
+    (``cta_group::2``: 256 x 256 tiles, each CTA staging half of the B tile) unless switched off here or with
+    ``SOAP_TP_GEMM_CTA_PAIRS=0``."""
+    _C.gemm_use_cta_pairs(bool(on))
+
+
+if os.environ.get("SOAP_TP_GEMM_CTA_PAIRS", "1") == "0":
+    use_cta_pairs(False)
+
+
 @dataclass
 class Planes:
     """Operand planes of a K x cols column-major matrix ``x``.

@@ -172,3 +172,118 @@ def test_mixed_output_planes_and_adam_epilogue():
     assert _rel(update.dense().cpu(), want) < 1e-4
     with pytest.raises(ValueError, match="both operands"):
         k.gemm(am, k.split_planes(b.cuda()), out=plain)
+
+
+@pytest.fixture
+def single_cta_reference():
+    """Runs a product once on CTA pairs (the default for large problems) and once on single CTAs."""
+    from soap_tp_b200.engine import kernels as k
+
+    def both(run):
+        results = []
+        for pairs in (True, False):
+            k.use_cta_pairs(pairs)
+            try:
+                results.append(run())
+            finally:
+                k.use_cta_pairs(True)
+        return results
+
+    return both
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+@pytest.mark.parametrize("K,M,N", [(1024, 2560, 2048), (520, 2500, 2100), (96, 4096, 2304)])
+def test_cta_pairs_store(K, M, N, mixed, single_cta_reference):
+    """256 x 256 tiles on CTA pairs (cta_group::2): ragged edges, padded pitch, EMA form, against fp64 and against the
+    single-CTA kernel (same MMA order and promotion cadence, hence the same bits)."""
+    from soap_tp_b200.engine import kernels as k
+
+    a, b = _operands(K, M, N, 21)
+    old = torch.randn(N + 1, M + 4, generator=torch.Generator().manual_seed(22))
+    expected = 0.25 * (a.double().T @ b.double()) + 0.5 * old.T[:M, :N].double()
+    ap, bp = k.split_planes(a.cuda(), mixed=mixed), k.split_planes(b.cuda(), mixed=mixed)
+
+    def run():
+        backing = old.cuda()
+        out = backing.T[:M, :N]
+        k.gemm(ap, bp, out=out, alpha=0.25, beta=0.5)
+        k.check_status()
+        assert torch.equal(backing[:, M:].cpu(), old[:, M:]) and torch.equal(backing[N:, :].cpu(), old[N:, :])
+        return out.cpu()
+
+    pair, single = single_cta_reference(run)
+    assert _rel(pair, expected) < 2e-6, _rel(pair, expected)
+    assert torch.equal(pair, single)
+
+
+def test_cta_pairs_symmetric_and_row_major(single_cta_reference):
+    from soap_tp_b200.engine import kernels as k
+
+    g = torch.Generator().manual_seed(23)
+    a = torch.randn(300, 2600, generator=g)
+    old = torch.randn(2600, 2600, generator=g)
+    old = old + old.T
+    expected = 0.9 * old.double() + 0.1 * (a.double().T @ a.double())
+    ap = k.split_planes(a.cuda())
+
+    def symmetric():
+        out = old.cuda().T.contiguous().T
+        k.gemm(ap, ap, out=out, alpha=0.1, beta=0.9, symmetric=True)
+        k.check_status()
+        assert torch.equal(out, out.T)
+        return out.cpu()
+
+    pair, single = single_cta_reference(symmetric)
+    assert _rel(pair, expected) < 2e-6
+    assert torch.equal(pair, single)
+    b = torch.randn(300, 2304, generator=g)
+    bp = k.split_planes(b.cuda())
+
+    def row_major():
+        out = torch.empty(2600, 2304, device="cuda")
+        k.gemm(ap, bp, mode=k.EPI_ROW_MAJOR, out=out, alpha=0.5)
+        k.check_status()
+        return out.cpu()
+
+    pair, single = single_cta_reference(row_major)
+    assert _rel(pair, 0.5 * (a.double().T @ b.double())) < 2e-6
+    assert torch.equal(pair, single)
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+def test_cta_pairs_split_and_adam_epilogues(mixed, single_cta_reference):
+    """The rotation chain of the optimizer step at a size that runs on CTA pairs: T = X^T Q written as operand planes,
+    then Adam in the eigenbasis fused into (Q^T X) R."""
+    from soap_tp_b200.engine import kernels as k
+
+    g = torch.Generator().manual_seed(24)
+    rows, cols = 2560, 2304
+    x = torch.randn(rows, cols, generator=g)
+    q = torch.randn(rows, rows, generator=g) / rows ** 0.5
+    r = torch.randn(cols, cols, generator=g) / cols ** 0.5
+    xp, qp, rp = (k.split_planes(t.cuda(), mixed=mixed) for t in (x, q, r))
+    m0 = torch.randn(cols, rows, generator=g)
+    v0 = torch.rand(cols, rows, generator=g)
+    adam = dict(beta1=0.9, beta2=0.99, eps=1e-6, bias_correction1=1 - 0.9**3, bias_correction2=1 - 0.99**3)
+
+    def run():
+        t_planes = k.Planes.empty(cols, rows, "cuda", mixed=mixed)
+        k.gemm(xp, qp, mode=k.EPI_SPLIT, out_planes=t_planes)            # T = X^T Q  (cols x rows)
+        y_planes = k.Planes.empty(rows, cols, "cuda", mixed=mixed)
+        mt, vt = m0.cuda().T, v0.cuda().T                                # rows x cols, column-major
+        k.gemm(t_planes, rp, mode=k.EPI_ADAM, out_planes=y_planes, momentum=mt, variance=vt, adam=adam)
+        k.check_status()
+        return t_planes.dense().cpu(), y_planes.dense().cpu(), mt.cpu(), vt.cpu()
+
+    pair, single = single_cta_reference(run)
+    expected_t = x.double().T @ q.double()
+    y = expected_t.T @ r.double()
+    em = 0.9 * m0.T.double() + 0.1 * y
+    ev = 0.99 * v0.T.double() + 0.01 * y * y
+    eu = (em / adam["bias_correction1"]) / (ev.sqrt() / adam["bias_correction2"] ** 0.5 + 1e-6)
+    assert _rel(pair[0], expected_t) < (1e-5 if mixed else 2e-6)
+    assert _rel(pair[2], em) < 2e-6 and _rel(pair[3], ev) < 6e-6
+    assert _rel(pair[1], eu) < 1e-5
+    for got, want in zip(pair, single):
+        assert torch.equal(got, want)
