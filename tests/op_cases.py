@@ -287,6 +287,52 @@ def case_soap_trajectory(rank, world, device_kind, shape, nb, grid, shard_dim, s
         assert state[name].dtype == torch.float32 and state[name].stride(0) == 1
 
 
+def case_soap_shared_basis(rank, world, device_kind, shape, nb, grid, shard_dim, steps, tolerance):
+    """``soap_step`` against the dense oracle with the ORACLE's eigenbases injected after the warm-up call.
+
+    With both implementations rotating into the same bases, nothing ill-conditioned separates them until the first
+    refresh: the bound is a plain ``tolerance`` that does not depend on the eigensolver under test or on a measured
+    noise floor.  The reference compares whole trajectories the same way (``tests/unit/test_soap.py:186-290``) but
+    has no mode that shares the bases."""
+    device = dev(device_kind, rank)
+    betas, pbeta, eps = (0.9, 0.95), 0.9, 1e-8
+    # float64 oracle: in float32 its own rounding (momentum and gradient are rotated by separate products there)
+    # already moves the update by 1e-5 through the entries whose rotated gradient nearly vanishes
+    oracle = DenseSOAP(shape, beta1=betas[0], beta2=betas[1], preconditioner_beta=pbeta, eps=eps,
+                       basis_refresh_interval=steps + 1, dtype=torch.float64)
+    state = {}
+    param_ref = torch.zeros(shape, dtype=torch.float64)
+    param_tp = torch.zeros(shape, dtype=torch.float64)
+    for it in range(steps):
+        G = seeded(shape, 300 + it, 2.0)
+        shard = G.chunk(world, dim=shard_dim)[rank].contiguous().to(device)
+        update = soap_step(shard, state, global_shape=shape, shard_dim=shard_dim, block_size=nb,
+                           process_grid_shape=grid, preconditioner_beta=pbeta, beta1=betas[0], beta2=betas[1],
+                           eps=eps, basis_refresh_interval=steps + 1, basis_implementation="eigh")
+        expected = oracle.step(G)
+        if it == 0:
+            assert float(update.abs().max()) == 0.0
+            oracle.QL, oracle.QR = oracle.QL.float().double(), oracle.QR.float().double()   # the very same numbers
+            state["left_basis"].copy_(pack(oracle.QL.float(), nb, grid, rank, device))
+            state["right_basis"].copy_(pack(oracle.QR.float(), nb, grid, rank, device))
+            continue
+        parts = [torch.empty_like(update.cpu()) for _ in range(world)]
+        dist.all_gather(parts, update.cpu().contiguous())
+        full = torch.cat(parts, dim=shard_dim)
+        param_ref -= expected.double()
+        param_tp -= full.double()
+        err_u, err_p = relative_l2(full.double(), expected), relative_l2(param_tp, param_ref)
+        if rank == 0:
+            print(f"{shape[0]}x{shape[1]} dim{shard_dim} shared bases | step {it} | SOAP relL2={err_u:.2e} | "
+                  f"PARAM relL2={err_p:.2e}", flush=True)
+        assert err_u <= tolerance, (it, err_u)
+        assert err_p <= tolerance, (it, err_p)
+    for side, (P, Q) in (("left", (oracle.L, oracle.QL)), ("right", (oracle.R, oracle.QR))):
+        got = unpack(state[f"{side}_preconditioner"], P.shape, nb, grid)
+        assert relative_l2(got.double(), P) <= tolerance, side
+        assert torch.equal(unpack(state[f"{side}_basis"], Q.shape, nb, grid), Q.float())   # untouched without a refresh
+
+
 def case_batch(rank, world, device_kind, specs):
     """Run several cases in one process group (process start-up dominates tiny cases).
     ``specs`` is a list of ``(function name, args)``; failures name the failing spec."""

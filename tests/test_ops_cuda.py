@@ -42,6 +42,17 @@ def test_single_gpu_trajectory():
     run_distributed(cases.case_batch, 1, "cuda", specs)
 
 
+def test_shared_basis_trajectory():
+    """The oracle's eigenbases injected after the warm-up call, so that the bound (1e-5, no noise floor) does not
+    depend on the eigensolver under test: 1 GPU and a (2, 2) grid, ragged and multi-block shapes."""
+    run_distributed(cases.case_batch, 1, "cuda", [
+        ("case_soap_shared_basis", ((20, 20), 2, (1, 1), 1, 6, 1e-5)),
+        ("case_soap_shared_basis", ((384, 260), 64, (1, 1), 0, 6, 1e-5))])
+    run_distributed(cases.case_batch, 4, "cuda", [
+        ("case_soap_shared_basis", ((12, 16), 3, (2, 2), 0, 6, 1e-5)),
+        ("case_soap_shared_basis", ((384, 256), 64, (2, 2), 1, 6, 1e-5))])
+
+
 GRID4 = (2, 2)
 
 

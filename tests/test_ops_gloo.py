@@ -61,3 +61,11 @@ def test_two_rank_grids():
         ("case_rotate", ((9, 13), 2, (1, 2))), ("case_gram", ((9, 13), 2, (2, 1), 0, 0.5)),
         ("case_refresh", ((8, 12), 2, (2, 1))), ("case_redistribute", ((12, 10), 3, (1, 2), 1)),
     ])
+
+
+def test_shared_basis_trajectory():
+    """The oracle's eigenbases injected after the warm-up call: every later step agrees to 1e-5 with no noise floor."""
+    run_distributed(cases.case_batch, 4, "cpu", [
+        ("case_soap_shared_basis", ((20, 20), 2, (2, 2), 1, 6, 1e-5)),
+        ("case_soap_shared_basis", ((12, 16), 3, (2, 2), 0, 6, 1e-5)),
+        ("case_soap_shared_basis", ((96, 64), 16, (2, 2), 1, 5, 1e-5))])

@@ -11,16 +11,16 @@ pytestmark = pytest.mark.gpu
 
 
 def _check(matrix: torch.Tensor, Q: torch.Tensor, tolerance: float) -> None:
-    a, q = matrix.double().cpu(), Q.double().cpu()
+    a, q = matrix.double(), Q.double()         # float64 products on the device
     n = a.shape[0]
-    orthogonality = float((q.T @ q - torch.eye(n, dtype=torch.float64)).abs().max())
+    orthogonality = float((q.T @ q - torch.eye(n, dtype=torch.float64, device=a.device)).abs().max())
     r = q.T @ a
     below = float(torch.tril(r, -1).norm() / a.norm().clamp_min(1e-30))
     assert orthogonality < tolerance, f"|Q^T Q - I|_max = {orthogonality}"
     assert below < tolerance, f"|tril(Q^T A)| / |A| = {below}"
 
 
-@pytest.mark.parametrize("n", [128, 200, 384, 1000, 2048])
+@pytest.mark.parametrize("n", [128, 200, 384, 1000, 2048, 8192])
 def test_householder_qr_properties(n):
     from soap_tp_b200.engine import kernels as k
     from soap_tp_b200.engine import qr
