@@ -20,6 +20,7 @@ Reported in one JSON line on rank 0:
 * ``median_steady_ms``, ``refresh_step_ms``, ``init_ms`` -- from one CUDA-event pair per step (maximum over
   ranks per step): the median step without a refresh, the mean step with one, and the first call (both
   eigenbases), which is outside the timed region;
+* ``host_enqueue_ms_median_steady`` -- host time the launching thread spends inside one steady ``soap_step`` call;
 * ``check`` -- correctness figures computed after the timed region (``--no-check`` skips them): orthogonality
   of both bases, both Gram matrices against a float64 EMA of the same gradient sequence, and a 2048 x 2048
   side problem on the same grid against the single-GPU pipeline (``soap_tp_b200/bench/checks.py``).
@@ -262,8 +263,11 @@ def run(args: argparse.Namespace) -> int:
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         fence()
         marks[0].record()
+        host_ms = []
         for i in range(args.steps):
+            host_begin = time.perf_counter()
             step_fn(resident[i % pool])
+            host_ms.append((time.perf_counter() - host_begin) * 1e3)
             marks[i + 1].record()
         fence()
         history.extend(counter + i % pool for i in range(args.steps))
@@ -271,6 +275,11 @@ def run(args: argparse.Namespace) -> int:
         dist.all_reduce(device_ms, op=dist.ReduceOp.MAX)
         per_step = max_over_ranks(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
         summary = step_summary(per_step, len(history) - args.steps)
+        # host time to enqueue one step (rank 0's median over the steps without a refresh): far below the device
+        # time means the device, not the launching thread, sets the pace
+        first = len(history) - args.steps
+        steady_host = [t for i, t in enumerate(host_ms) if (first + i) % args.refresh_interval]
+        summary["host_enqueue_ms_median_steady"] = round(statistics.median(steady_host), 3) if steady_host else None
         launches_timed = launches() - launches_before
         if args.impl == "ours" and args.stage_timing:
             stages = GLOBAL_STAGE_TIMER.summary()

@@ -127,7 +127,7 @@ def _long_leader_work_is_awaited_on_the_host(rank, world):
             self.world, self.rank, self.control = world, rank, dist.group.WORLD
             self.use_device_barrier, self.barrier_count = True, 0
             self._epochs, self._channel_stride = [0] * self.CHANNELS, 64
-            self.device, self.barrier_timeout_s = torch.device("cpu"), 0.2
+            self.device, self.barrier_timeout_s = torch.device("cpu"), 0.75
             self.arrivals = []
 
     recorder = Recorder()
@@ -147,13 +147,13 @@ def _long_leader_work_is_awaited_on_the_host(rank, world):
     torch.cuda.current_stream = lambda *a, **k: type("S", (), {"synchronize": lambda self: None, "cuda_stream": 0})()
     try:
         if rank == 0:
-            time.sleep(1.0)        # the "leader" is still factoring
+            time.sleep(2.0)        # the "leader" is still factoring
         recorder.barrier(after_long_work=True)
     finally:
         kernels.status_word, kernels._count, torch.cuda.current_stream = original_status, original_count, original_sync
     stamps = [None] * world
     dist.all_gather_object(stamps, recorder.arrivals[0])
-    # every rank reached the device barrier within the spin budget of the others, although rank 0 was 1 s late
+    # every rank reached the device barrier within the spin budget of the others, although rank 0 was 2 s late
     assert max(stamps) - min(stamps) < recorder.barrier_timeout_s, stamps
 
 
