@@ -176,6 +176,7 @@ def run(args: argparse.Namespace) -> int:
         raise SystemExit(f"size {size} must be divisible by {world} ranks")
     shard_shape = (size // world, size) if args.shard_dim == 0 else (size, size // world)
 
+    status_wait_seconds = lambda: 0.0
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT / "baseline"))
         import reference_arm
@@ -198,6 +199,7 @@ def run(args: argparse.Namespace) -> int:
         step_fn = make_step(size, state)
 
         launches = kernels.total_launches
+        status_wait_seconds = lambda: kernels._StatusMonitor.waited_seconds
         if args.stage_timing:
             from soap_tp_b200.profiling import GLOBAL_STAGE_TIMER
 
@@ -265,9 +267,9 @@ def run(args: argparse.Namespace) -> int:
         marks[0].record()
         host_ms = []
         for i in range(args.steps):
-            host_begin = time.perf_counter()
+            host_begin, waited = time.perf_counter(), status_wait_seconds()
             step_fn(resident[i % pool])
-            host_ms.append((time.perf_counter() - host_begin) * 1e3)
+            host_ms.append((time.perf_counter() - host_begin - (status_wait_seconds() - waited)) * 1e3)
             marks[i + 1].record()
         fence()
         history.extend(counter + i % pool for i in range(args.steps))
@@ -275,8 +277,9 @@ def run(args: argparse.Namespace) -> int:
         dist.all_reduce(device_ms, op=dist.ReduceOp.MAX)
         per_step = max_over_ranks(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
         summary = step_summary(per_step, len(history) - args.steps)
-        # host time to enqueue one step (rank 0's median over the steps without a refresh): far below the device
-        # time means the device, not the launching thread, sets the pace
+        # host time to enqueue one step (rank 0's median over the steps without a refresh), without the wait for the
+        # previous step's status word: far below the device time means the device, not the launching thread, sets
+        # the pace
         first = len(history) - args.steps
         steady_host = [t for i, t in enumerate(host_ms) if (first + i) % args.refresh_interval]
         summary["host_enqueue_ms_median_steady"] = round(statistics.median(steady_host), 3) if steady_host else None

@@ -484,6 +484,17 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
           // A 128-byte row of the bf16 plane: hb of the 32 k-elements in bytes 0..63, lb in bytes 64..127.  The two
           // correction products as bf16 MMAs (16 elements of K = 32 bytes each), then hi*hi in tf32.
           constexpr uint64_t kLb = 64 >> 4;
+          // Even k-blocks issue the bf16 products first, odd ones the tf32 products, so that the tensor core changes
+          // kind once per k-block instead of twice.
+          const bool tf32_first = (kb & 1) != 0;
+          if (tf32_first) {
+#pragma unroll
+            for (int k = 0; k < kBK / 8; ++k) {
+              const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+              umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, first ? 0u : 1u);
+              first = 0;
+            }
+          }
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
@@ -491,10 +502,12 @@ gemm_tf32x3_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant_
             first = 0;
             umma_bf16_ss(tmem_acc, a_hl + adv, b_hl + kLb + adv, idesc16, 1);                    // hi * lo
           }
+          if (!tf32_first) {
 #pragma unroll
-          for (int k = 0; k < kBK / 8; ++k) {
-            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
-            umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+            for (int k = 0; k < kBK / 8; ++k) {
+              const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+              umma_tf32_ss(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+            }
           }
           umma_commit(&empty_bar[s]);
           continue;
@@ -708,6 +721,15 @@ gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ 
         const uint64_t b_2 = umma_desc_kmajor<kRowBytes>(stage + 2 * kBM * kRowBytes + (BN / 2) * kRowBytes);
         if constexpr (MIXED) {
           constexpr uint64_t kLb = 64 >> 4;
+          const bool tf32_first = (kb & 1) != 0;     // one change of MMA kind per k-block, as in the single-CTA kernel
+          if (tf32_first) {
+#pragma unroll
+            for (int k = 0; k < kBK / 8; ++k) {
+              const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+              umma_tf32_ss_pair(tmem_acc, a_hi + adv, b_hi + adv, idesc, first ? 0u : 1u);
+              first = 0;
+            }
+          }
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
@@ -715,10 +737,12 @@ gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ 
             first = 0;
             umma_bf16_ss_pair(tmem_acc, a_2 + adv, b_2 + kLb + adv, idesc16, 1);                   // hi * lo
           }
+          if (!tf32_first) {
 #pragma unroll
-          for (int k = 0; k < kBK / 8; ++k) {
-            const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
-            umma_tf32_ss_pair(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+            for (int k = 0; k < kBK / 8; ++k) {
+              const uint64_t adv = static_cast<uint64_t>(k * 32 >> 4);
+              umma_tf32_ss_pair(tmem_acc, a_hi + adv, b_hi + adv, idesc, 1);
+            }
           }
         } else {
 #pragma unroll

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import math
 import os
+import time
 from dataclasses import dataclass
 from typing import Dict, Optional
 
@@ -88,6 +89,8 @@ class _StatusMonitor:
     """Deferred read-back of one device's status word: a 4-byte copy into pinned memory per step, looked at
     one step later, so that a timed-out wait surfaces as an exception without a device synchronisation."""
 
+    waited_seconds = 0.0      # host time spent waiting for the previous step's copy (all devices of the process)
+
     def __init__(self, index: int, on_device: bool = True) -> None:
         self.index = index
         self.host = torch.zeros(2, dtype=torch.int32)
@@ -102,7 +105,10 @@ class _StatusMonitor:
         previous = 1 - self.turn
         if self.pending[previous]:
             if self.events is not None:
-                self.events[previous].synchronize()   # recorded a whole step ago: already complete
+                # recorded a whole step ago: complete unless the host runs a full step ahead of the device
+                begin = time.perf_counter()
+                self.events[previous].synchronize()
+                _StatusMonitor.waited_seconds += time.perf_counter() - begin
             self.pending[previous] = False
             code = int(self.host[previous])
             if code != 0:
