@@ -42,7 +42,8 @@ PYBIND11_MODULE(_C, m) {
          int64_t c_batch_stride, int64_t a_k_total, int64_t a_rows_total, int64_t b_k_total, int64_t b_rows_total,
          uint64_t remap, uint64_t C2hi, uint64_t C2lo, int64_t ld2, int m_limit, int o1_row_start, int tri_nb,
          int tri_pr, int tri_Pr, int tri_pc, int tri_Pc, int tri_m0, int tri_n0, uint64_t a_hl, int64_t lda16,
-         uint64_t b_hl, int64_t ldb16, uint64_t Chl, int64_t ldp16) {
+         uint64_t b_hl, int64_t ldb16, uint64_t Chl, int64_t ldp16, uint64_t push_table, int64_t push_ld,
+         int64_t push_ld16, int push_nb, int push_Pr, int push_Pc, int push_pr, int push_pc, int push_mixed) {
         GemmOperands ops{};
         ops.a_hi = ptr<const float>(a_hi); ops.a_lo = ptr<const float>(a_lo); ops.lda = lda;
         ops.b_hi = ptr<const float>(b_hi); ops.b_lo = ptr<const float>(b_lo); ops.ldb = ldb;
@@ -67,6 +68,9 @@ PYBIND11_MODULE(_C, m) {
         ops.a_hl = ptr<const uint16_t>(a_hl); ops.lda16 = lda16;
         ops.b_hl = ptr<const uint16_t>(b_hl); ops.ldb16 = ldb16;
         prob.Chl = ptr<uint16_t>(Chl); prob.ldp16 = ldp16;
+        prob.push_table = ptr<const uint64_t>(push_table); prob.push_ld = push_ld; prob.push_ld16 = push_ld16;
+        prob.push_nb = push_nb; prob.push_Pr = push_Pr; prob.push_Pc = push_Pc; prob.push_pr = push_pr;
+        prob.push_pc = push_pc; prob.push_mixed = push_mixed;
         py::gil_scoped_release release;
         gemm_tf32x3(ops, prob, ptr<int>(status), stream_of(stream));
       },
@@ -81,7 +85,9 @@ PYBIND11_MODULE(_C, m) {
       py::arg("C2hi") = 0, py::arg("C2lo") = 0, py::arg("ld2") = 0, py::arg("m_limit") = 0, py::arg("o1_row_start") = 0, py::arg("tri_nb") = 1, py::arg("tri_pr") = 0,
       py::arg("tri_Pr") = 1, py::arg("tri_pc") = 0, py::arg("tri_Pc") = 1, py::arg("tri_m0") = 0, py::arg("tri_n0") = 0,
       py::arg("a_hl") = 0, py::arg("lda16") = 0, py::arg("b_hl") = 0, py::arg("ldb16") = 0, py::arg("Chl") = 0,
-      py::arg("ldp16") = 0,
+      py::arg("ldp16") = 0, py::arg("push_table") = 0, py::arg("push_ld") = 0, py::arg("push_ld16") = 0,
+      py::arg("push_nb") = 1, py::arg("push_Pr") = 1, py::arg("push_Pc") = 1, py::arg("push_pr") = 0,
+      py::arg("push_pc") = 0, py::arg("push_mixed") = 0,
       "3xTF32 tcgen05 GEMM acc[m,n] = sum_k Za[k,m] Zb[k,n] with fused epilogue");
 
   m.def("gemm_use_cta_pairs", [](bool on) { gemm_use_cta_pairs(on); },

@@ -12,6 +12,9 @@ enum EpilogueMode : int {
   kEpiRowMajor = 3,  // C[m*ldc + n] = alpha*acc (tensor-parallel shard output)
   kEpiPairUpdate = 4,  // block-Jacobi column-pair update: the 128 result columns of a batch item go, in two
                        // halves of 64, to new column positions; written as planes in both orientations
+  kEpiPush = 5,      // GEMM -> all-gather in one kernel: the result tile is this rank's block of a 2-D block-cyclic
+                     // matrix T; every element alpha*acc is stored, as operand planes, straight into the gathered
+                     // operand T[:, row class] of every rank that consumes it (peer memory over NVLink included)
 };
 
 // Operand planes.  a_* is the K x M column-major matrix Za (pitch lda floats), b_* the K x N matrix Zb.
@@ -72,6 +75,14 @@ struct GemmProblem {
   int64_t ld2;
   int m_limit;
   int o1_row_start;            // rows m < o1_row_start are not written in the first orientation
+  // kEpiPush.  Local element (m, n) is T(i, j) with i = ((m / nb) * Pr + pr) * nb + m % nb and
+  // j = ((n / nb) * Pc + pc) * nb + n % nb.  Its consumers are the ranks of grid row (j / nb) % Pr; in their planes
+  // (depth index i, column c = ((j / nb) / Pr) * nb + j % nb) it lands at hi[c * push_ld + i] and in the low plane
+  // (fp32 lo at the same offset, or the interleaved bf16 plane at c * push_ld16 + bf16_plane_index(i)).
+  const uint64_t* push_table = nullptr;   // device array [Pr * Pc][2]: hi plane and low plane of rank pr' * Pc + pc'
+  int64_t push_ld = 0, push_ld16 = 0;
+  int push_nb = 1, push_Pr = 1, push_Pc = 1, push_pr = 0, push_pc = 0;
+  int push_mixed = 0;                     // 1: the low plane is the interleaved bf16 plane
 };
 
 // acc[m, n] = sum_k Za[k, m] * Zb[k, n] on tcgen05 with 3xTF32 compensation, then the epilogue.

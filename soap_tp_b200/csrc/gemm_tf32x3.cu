@@ -111,6 +111,19 @@ __device__ __forceinline__ int global_col(const GemmProblem& p, int n) {
   return ((n / p.tri_nb) * p.tri_Pc + p.tri_pc) * p.tri_nb + n % p.tri_nb;
 }
 
+// kEpiPush: where local element (m, n) goes in its consumers' planes.
+struct PushTarget {
+  int grid_row;      // pr' of the consuming ranks
+  int64_t column;    // column of their gathered operand
+};
+__device__ __forceinline__ PushTarget push_target(const GemmProblem& p, int n) {
+  const int jb = (n / p.push_nb) * p.push_Pc + p.push_pc;
+  return PushTarget{jb % p.push_Pr, static_cast<int64_t>(jb / p.push_Pr) * p.push_nb + n % p.push_nb};
+}
+__device__ __forceinline__ int64_t push_depth(const GemmProblem& p, int m) {
+  return static_cast<int64_t>((m / p.push_nb) * p.push_Pr + p.push_pr) * p.push_nb + m % p.push_nb;
+}
+
 constexpr int kTilePitch = kBM + 4;   // floats between columns of the staged tile (keeps 16-byte alignment)
 
 struct Vec4 {
@@ -168,6 +181,22 @@ __device__ __forceinline__ void epilogue_scalar(const GemmProblem& prob, int64_t
       }
     }
     if (prob.C) prob.C[m + static_cast<int64_t>(n) * prob.ldc] = u;
+  } else if constexpr (MODE == kEpiPush) {
+    const PushTarget t = push_target(prob, n);
+    const int64_t i = push_depth(prob, m);
+    const float v = prob.alpha * acc;
+    const float hi = tf32_round(v);
+    for (int pc = 0; pc < prob.push_Pc; ++pc) {
+      const uint64_t* entry = prob.push_table + 2 * (t.grid_row * prob.push_Pc + pc);
+      reinterpret_cast<float*>(entry[0])[t.column * prob.push_ld + i] = hi;
+      if (prob.push_mixed) {
+        uint16_t* low = reinterpret_cast<uint16_t*>(entry[1]) + t.column * prob.push_ld16 + bf16_plane_index(i);
+        low[0] = bf16_bits(v);
+        low[32] = bf16_bits(v - hi);
+      } else {
+        reinterpret_cast<float*>(entry[1])[t.column * prob.push_ld + i] = v - hi;
+      }
+    }
   }
 }
 
@@ -247,6 +276,28 @@ __device__ __forceinline__ void epilogue_store4(const GemmProblem& prob, int64_t
       }
     }
     if (prob.C) store4(prob.C + m + static_cast<int64_t>(n) * prob.ldc, u);
+  } else if constexpr (MODE == kEpiPush) {
+    // four consecutive local rows are four consecutive depth indices (block sizes are multiples of 4)
+    const PushTarget t = push_target(prob, n);
+    const int64_t i = push_depth(prob, m);
+    Vec4 hi, lo, plain;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      plain.v[r] = prob.alpha * acc.v[r];
+      hi.v[r] = tf32_round(plain.v[r]);
+      lo.v[r] = plain.v[r] - hi.v[r];
+    }
+    for (int pc = 0; pc < prob.push_Pc; ++pc) {
+      const uint64_t* entry = prob.push_table + 2 * (t.grid_row * prob.push_Pc + pc);
+      store4(reinterpret_cast<float*>(entry[0]) + t.column * prob.push_ld + i, hi);
+      if (prob.push_mixed) {
+        uint16_t* low = reinterpret_cast<uint16_t*>(entry[1]) + t.column * prob.push_ld16 + bf16_plane_index(i);
+        store4_bf16(low, plain.v);
+        store4_bf16(low + 32, lo.v);
+      } else {
+        store4(reinterpret_cast<float*>(entry[1]) + t.column * prob.push_ld + i, lo);
+      }
+    }
   }
 }
 
@@ -277,6 +328,8 @@ __device__ __forceinline__ void run_epilogue(const GemmProblem& prob, const floa
   if constexpr (MODE == kEpiAdam)
     vector = vector && aligned16(prob.mom, prob.ldm) && aligned16(prob.var, prob.ldv) && aligned16(prob.Chi, prob.ldp) &&
              aligned16(prob.Clo, prob.ldp) && aligned16(prob.C, prob.ldc);
+  if constexpr (MODE == kEpiPush)   // plane bases are segment starts (256-byte aligned); pitches and block size decide
+    vector = vector && (prob.push_nb & 3) == 0 && (prob.push_ld & 3) == 0 && (prob.push_ld16 & 3) == 0;
   if (!vector) {
     for (int nl = ew; nl < cols; nl += kEpiWarps) {
       const int n = n0 + nl;
@@ -921,6 +974,9 @@ void gemm_use_cta_pairs(bool on) { g_use_pairs = on; }
 
 void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, cudaStream_t stream) {
   if (prob.M <= 0 || prob.N <= 0) return;
+  if (prob.mode == kEpiPush && (prob.push_table == nullptr || prob.push_nb < 1 || prob.push_Pr < 1 || prob.push_Pc < 1 ||
+                                prob.k_splits > 1 || prob.batches > 1 || prob.symmetric))
+    throw std::invalid_argument("gemm_tf32x3: the push epilogue needs a target table and a plain (unsplit, unbatched) product");
   if (prob.K <= 0) throw std::invalid_argument("gemm_tf32x3 needs K >= 1");
   // Wide tiles when there are enough of them to fill the 148 SMs; narrower tiles otherwise.
   const int64_t wide_tiles = static_cast<int64_t>((prob.M + kBM - 1) / kBM) * ((prob.N + 255) / 256);
@@ -948,6 +1004,7 @@ void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, 
       case kEpiSplit: SOAP_PAIR_LAUNCH(kEpiSplit); return;
       case kEpiAdam: SOAP_PAIR_LAUNCH(kEpiAdam); return;
       case kEpiRowMajor: SOAP_PAIR_LAUNCH(kEpiRowMajor); return;
+      case kEpiPush: SOAP_PAIR_LAUNCH(kEpiPush); return;
       default: break;
     }
 #undef SOAP_PAIR_LAUNCH
@@ -964,6 +1021,9 @@ void gemm_tf32x3(const GemmOperands& ops, const GemmProblem& prob, int* status, 
       break;
     case kEpiRowMajor:
       SOAP_GEMM_LAUNCH(kEpiRowMajor);
+      break;
+    case kEpiPush:
+      SOAP_GEMM_LAUNCH(kEpiPush);
       break;
     case kEpiPairUpdate:
       if (prob.N != 128 || prob.remap == nullptr || prob.Chi == nullptr)

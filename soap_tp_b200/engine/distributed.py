@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import math
 import os
+import weakref
 from dataclasses import dataclass
 from typing import Any, Dict, MutableMapping, Optional, Tuple
 
@@ -40,6 +41,13 @@ PIPELINE_GATHERS = os.environ.get("SOAP_TP_PIPELINE_GATHERS", "0") == "1"
 DISTRIBUTED_QR = os.environ.get("SOAP_TP_DISTRIBUTED_QR", "1") != "0"
 # SOAP_TP_OVERLAP_GRAM=0: the Gram EMAs run after the rotations on the same stream instead of beside them
 OVERLAP_GRAM = os.environ.get("SOAP_TP_OVERLAP_GRAM", "1") != "0"
+# SOAP_TP_PUSH_PRODUCTS=1: the first product of every two-sided product stores its result, split into operand
+# planes, straight into the gathered operand of the ranks that run the second product (peer stores from the GEMM
+# epilogue: GEMM -> all-gather in one kernel, no pull kernel in between).  Off by default: at 8192 on 4 B200s the steady
+# step measured 6.57 ms against 6.27 ms with the pull (the epilogue then stores 16 bytes per element, half of them
+# over NVLink, in the part of a tile that no other work of its CTA overlaps; the pull kernel streams the same bytes
+# at 600-700 GB/s), and 11.35 against 11.34 ms on 2 GPUs.
+PUSH_PRODUCTS = os.environ.get("SOAP_TP_PUSH_PRODUCTS", "0") == "1"
 # output tiles a chunk must keep (about one wave of the 148 SMs); tests lower it to chunk small problems
 PIPELINE_MIN_TILES = max(1, int(os.environ.get("SOAP_TP_PIPELINE_MIN_TILES", "120")))
 
@@ -190,8 +198,11 @@ class GridEngine:
         i.e. rows of ``Q`` in my column class.  Collective; cached on the tensor version."""
         entry = self._basis_cache.setdefault((Q.data_ptr(), size), {})
         # Ranks run the same program on the same step, so staleness is decided locally: a basis
-        # changes on all ranks (refresh, initialisation, checkpoint load) or on none.
-        if entry.get("key") == (Q._version, size):
+        # changes on all ranks (refresh, initialisation, checkpoint load) or on none.  The entry belongs to one
+        # tensor OBJECT: a new tensor that the allocator happens to place at the address of a freed one (with
+        # the same version count) must miss on every rank, or the ranks would disagree about the barriers below.
+        owner = entry.get("owner")
+        if owner is not None and owner() is Q and entry.get("key") == (Q._version, size):
             return entry["plain"], entry["transposed"]
         source = self.stage_packed("basis", Q, (size, size))
         self.comm.barrier()
@@ -201,7 +212,7 @@ class GridEngine:
         dist_gather(source, IDENTITY, self.col_map(), size, cols, planes=plain)
         dist_gather(source, IDENTITY, self.col_map(), size, cols, transpose=True, planes=transposed)
         self.comm.barrier()
-        entry.update(key=(Q._version, size), plain=plain, transposed=transposed)
+        entry.update(key=(Q._version, size), plain=plain, transposed=transposed, owner=weakref.ref(Q))
         return plain, transposed
 
     def side_stream(self) -> "torch.cuda.Stream":
@@ -281,19 +292,32 @@ class GridEngine:
         """
         rows, cols = shape
         a = panel if panel is not None else self.planes("panel_a", rows, self.rows_of(cols))
-        _, t_view, t_source = self.packed_segment("middle", (cols, rows))
         first_cols = max(1, first.cols)
+        push = PUSH_PRODUCTS and not PIPELINE_GATHERS
+        if push:
+            # GEMM -> all-gather in one kernel: the epilogue of the first product stores every element of the middle
+            # matrix, already split into operand planes, into the gathered operand of each rank that consumes it
+            ta, targets = self.push_targets(cols, rows)
 
-        def middle(c0: int, c1: int) -> None:
-            k.gemm(a.sub(0, c0, rows, c1 - c0), first, mode=k.EPI_STORE, out=t_view[c0:c1, :first_cols])
+            def middle(c0: int, c1: int) -> None:
+                k.gemm(a.sub(0, c0, rows, c1 - c0), first, mode=k.EPI_PUSH, push=targets)
+        else:
+            _, t_view, t_source = self.packed_segment("middle", (cols, rows))
+
+            def middle(c0: int, c1: int) -> None:
+                k.gemm(a.sub(0, c0, rows, c1 - c0), first, mode=k.EPI_STORE, out=t_view[c0:c1, :first_cols])
 
         if a.cols > 0:
             if gathered:
                 middle(0, a.cols)
+            elif push:
+                dist_gather(source, IDENTITY, self.row_map(), rows, a.cols, planes=a)
+                middle(0, a.cols)
             else:
                 self.gather_then_multiply(source, self.row_map(), rows, a.cols, a, middle, other_cols=first.cols)
         self.comm.barrier()
-        ta = self.planes("panel_t", cols, self.rows_of(rows))
+        if not push:
+            ta = self.planes("panel_t", cols, self.rows_of(rows))
 
         def last(c0: int, c1: int) -> None:
             window = dict(final)
@@ -303,8 +327,46 @@ class GridEngine:
             k.gemm(ta.sub(0, c0, cols, c1 - c0), second, **window)
 
         if ta.cols > 0:
-            self.gather_then_multiply(t_source, self.row_map(), cols, ta.cols, ta, last, other_cols=second.cols)
+            if push:
+                last(0, ta.cols)
+            else:
+                self.gather_then_multiply(t_source, self.row_map(), cols, ta.cols, ta, last, other_cols=second.cols)
         return a
+
+    def push_targets(self, depth: int, width: int) -> Tuple[k.Planes, dict]:
+        """Operand planes of ``T[:, my row class]`` (``depth x rows_of(width)``) in symmetric memory, for the producers
+        of ``T`` to fill through peer pointers, and the argument dictionary of the pushing product.  Two sets
+        alternate from call to call: a rank may still be reading one set in the second product of a call while a
+        faster peer, one barrier further, already pushes the next call's middle matrix."""
+        self._push_calls = getattr(self, "_push_calls", 0) + 1
+        parity = self._push_calls % 2
+        mixed = k.MIXED_CORRECTIONS
+        most = max(1, numroc(width, self.nb, 0, self.Pr))
+        ld = max(4, k.round_up(depth, 4))
+        ld16 = 2 * k.round_up(max(1, depth), 32)
+        low_floats = most * (ld16 // 2 if mixed else ld)
+        name = f"push{parity}:{depth}x{width}:{self.nb}:{self.Pr}x{self.Pc}:{int(mixed)}"
+        fresh = name not in self.comm.segments
+        segment = self.comm.segment(name, most * ld + low_floats)
+        if fresh:
+            segment.local.zero_()          # the bf16 plane's tail past `depth` has to read as zeros
+            self.comm.barrier()            # ... before any peer starts to push into it
+        hi = segment.local[: most * ld].view(most, ld)
+        low = segment.local[most * ld: most * ld + low_floats]
+        mine = self.rows_of(width)
+        if mixed:
+            planes = k.Planes(hi, None, depth, mine, ld, low.view(torch.bfloat16).view(most, ld16), ld16)
+        else:
+            planes = k.Planes(hi, low.view(most, ld), depth, mine, ld)
+        key = ("push_table", name)
+        table = self._leader_tables.get(key)
+        if table is None:
+            entries = []
+            for base in segment.peer_ptrs:
+                entries += [base, base + 4 * most * ld]
+            table = self._leader_tables[key] = torch.tensor(entries, dtype=torch.int64, device=self.device)
+        return planes, dict(table=table, ld=ld, ld16=ld16, nb=self.nb, Pr=self.Pr, Pc=self.Pc, pr=self.pr, pc=self.pc,
+                            mixed=mixed)
 
 
 _ENGINES: Dict[tuple, GridEngine] = {}

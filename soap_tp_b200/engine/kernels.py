@@ -24,7 +24,7 @@ except ImportError:  # pragma: no cover - build on first use
     build_ext.build()
     from .. import _C  # type: ignore[attr-defined]
 
-EPI_STORE, EPI_SPLIT, EPI_ADAM, EPI_ROW_MAJOR, EPI_PAIR_UPDATE = 0, 1, 2, 3, 4
+EPI_STORE, EPI_SPLIT, EPI_ADAM, EPI_ROW_MAJOR, EPI_PAIR_UPDATE, EPI_PUSH = 0, 1, 2, 3, 4, 5
 
 STATUS_MESSAGES = {
     1: "GEMM consumer timed out waiting for a TMA stage",
@@ -278,11 +278,14 @@ def gemm(
     split_stride: int = 0,
     batch: Optional[dict] = None,
     lower_of_grid: Optional[tuple] = None,
+    push: Optional[dict] = None,
 ) -> None:
     """``acc[m, n] = sum_k a[k, m] * b[k, n]`` then the fused epilogue (see ``csrc/gemm.h``).
 
     ``out`` is a column-major ``M x N`` view for ``EPI_STORE`` (and the optional plain copy of
-    ``EPI_SPLIT``/``EPI_ADAM``) or a row-major ``M x N`` tensor for ``EPI_ROW_MAJOR``.
+    ``EPI_SPLIT``/``EPI_ADAM``) or a row-major ``M x N`` tensor for ``EPI_ROW_MAJOR``.  ``EPI_PUSH`` writes no
+    local output: ``push`` = ``dict(table, ld, ld16, nb, Pr, Pc, pr, pc, mixed)`` names the operand planes of the
+    consuming ranks (``csrc/gemm.h``, ``kEpiPush``), which the epilogue fills through peer pointers.
     """
     if batch is None:
         assert a.depth == b.depth, (a.depth, b.depth)
@@ -322,11 +325,18 @@ def gemm(
         ldv = variance.stride(1) if variance.shape[1] > 1 else max(1, variance.shape[0])
         b1, b2, eps = adam["beta1"], adam["beta2"], adam["eps"]
         ibc1, isbc2 = 1.0 / adam["bias_correction1"], 1.0 / math.sqrt(adam["bias_correction2"])
+    push_arguments = {}
+    if mode == EPI_PUSH:
+        assert push is not None and batch is None and k_splits == 1 and not symmetric
+        push_arguments = dict(push_table=push["table"].data_ptr(), push_ld=int(push["ld"]), push_ld16=int(push["ld16"]),
+                              push_nb=int(push["nb"]), push_Pr=int(push["Pr"]), push_Pc=int(push["Pc"]),
+                              push_pr=int(push["pr"]), push_pc=int(push["pc"]), push_mixed=int(bool(push["mixed"])))
     status = status_word(a.hi.device)
     _C.gemm_tf32x3(a.hi.data_ptr(), a.low_pointers()["lo"], a.ld, b.hi.data_ptr(), b.low_pointers()["lo"], b.ld, M, N, K,
                    mode, 2 if lower_of_grid is not None else int(symmetric), int(force_narrow), float(alpha), float(beta), c_ptr, ldc, chi, clo, ldp,
                    mom, var, ldm, ldv, b1, b2, eps, ibc1, isbc2, int(k_splits), int(split_stride), status.data_ptr(),
-                   _stream(), **_batch_arguments(a, b, batch), **_triangle_arguments(lower_of_grid), **mixed_arguments)
+                   _stream(), **_batch_arguments(a, b, batch), **_triangle_arguments(lower_of_grid), **mixed_arguments,
+                   **push_arguments)
     mark_written(out, momentum, variance)
     _count("gemm_tf32x3_kernel")
 

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import math
 import os
+import weakref
 from collections import OrderedDict
 from typing import Any, Dict, MutableMapping, Optional, Tuple
 
@@ -34,12 +35,15 @@ class BasisPlanes:
 
     def __init__(self) -> None:
         self.key: Optional[tuple] = None
+        self.owner = None                           # weak reference to the tensor object the planes were made from
         self.plain: Optional[k.Planes] = None       # operand Q   (depth = rows of Q)
         self.transposed: Optional[k.Planes] = None  # operand Q^T (depth = cols of Q)
 
     def refresh(self, Q: Tensor, size: int) -> None:
         key = (Q.data_ptr(), Q._version, size)
-        if key == self.key:
+        # the planes belong to one tensor OBJECT: a new tensor at a recycled address with the same version count
+        # (a freshly loaded checkpoint, a test's next case) must not be taken for the old one
+        if key == self.key and self.owner is not None and self.owner() is Q:
             return
         view = Q[:size, :size]
         if self.plain is not None and (self.plain.depth != size or self.plain.hi.device != Q.device):
@@ -47,6 +51,7 @@ class BasisPlanes:
         self.plain = k.split_planes(view, out=self.plain, mixed=k.MIXED_CORRECTIONS)
         self.transposed = k.split_planes(view, transpose=True, out=self.transposed, mixed=k.MIXED_CORRECTIONS)
         self.key = (Q.data_ptr(), Q._version, size)
+        self.owner = weakref.ref(Q)
 
 
 class ParameterContext:

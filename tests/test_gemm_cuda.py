@@ -287,3 +287,44 @@ def test_cta_pairs_split_and_adam_epilogues(mixed, single_cta_reference):
     assert _rel(pair[1], eu) < 1e-5
     for got, want in zip(pair, single):
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+@pytest.mark.parametrize("I,J,nb,grid,K", [(300, 260, 4, (2, 2), 96), (2560, 2304, 128, (2, 2), 200), (520, 390, 64, (2, 4), 64),
+                                           (384, 384, 128, (1, 2), 40)])
+def test_push_epilogue_fills_the_consumers_planes(I, J, nb, grid, K, mixed):
+    """GEMM -> all-gather in the epilogue: every rank of a grid (run one after the other on this GPU) computes its
+    block of the block-cyclic matrix T = A^T B and stores it, as operand planes, into the gathered operand
+    T[:, row class] of the ranks of the consuming grid row; afterwards every rank's planes hold exactly that."""
+    from soap_tp_b200.engine import kernels as k
+    from soap_tp_b200.layout import owned_indices
+
+    Pr, Pc = grid
+    a, b = _operands(K, I, J, 31)
+    expected = (a.double().T @ b.double())                       # T, I x J
+    most = max(len(owned_indices(J, nb, p, Pr)) for p in range(Pr))
+    ld, ld16 = max(4, k.round_up(I, 4)), 2 * k.round_up(I, 32)
+    targets, entries = [], []
+    for rank in range(Pr * Pc):
+        hi = torch.full((most, ld), float("nan"), device="cuda")
+        low = torch.zeros((most, ld16), dtype=torch.bfloat16, device="cuda") if mixed else torch.full((most, ld), float("nan"), device="cuda")
+        targets.append((hi, low))
+        entries += [hi.data_ptr(), low.data_ptr()]
+    table = torch.tensor(entries, dtype=torch.int64, device="cuda")
+    for pr in range(Pr):
+        for pc in range(Pc):
+            rows, cols = owned_indices(I, nb, pr, Pr), owned_indices(J, nb, pc, Pc)
+            if not (len(rows) and len(cols)):
+                continue
+            ap = k.split_planes(a[:, rows].contiguous().cuda(), mixed=mixed)
+            bp = k.split_planes(b[:, cols].contiguous().cuda(), mixed=mixed)
+            k.gemm(ap, bp, mode=k.EPI_PUSH, push=dict(table=table, ld=ld, ld16=ld16, nb=nb, Pr=Pr, Pc=Pc, pr=pr, pc=pc,
+                                                        mixed=mixed))
+    k.check_status()
+    for pr in range(Pr):
+        wanted = owned_indices(J, nb, pr, Pr)
+        for pc in range(Pc):
+            hi, low = targets[pr * Pc + pc]
+            planes = k.Planes(hi, None, I, len(wanted), ld, low, ld16) if mixed else k.Planes(hi, low, I, len(wanted), ld)
+            got = planes.dense().cpu()                            # I x len(wanted)
+            assert _rel(got, expected[:, wanted]) < (1e-5 if mixed else 2e-6), (pr, pc)

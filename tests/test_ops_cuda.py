@@ -112,3 +112,17 @@ def test_chunked_gather_product_pipeline(monkeypatch):
             ("case_gram", ((600, 520), 64, grid, 1, 0.25)), ("case_gram", ((520, 650), 128, grid, 0, 0.5)),
             ("case_rotate", ((520, 650), 64, grid)),
             ("case_soap_trajectory", ((384, 384), 64, grid, 1) + big)])
+
+
+def test_push_products(monkeypatch):
+    """The first product of every two-sided product pushes its result into the consumers' operand planes through
+    peer pointers (GEMM -> all-gather in the epilogue) instead of being pulled: rotations, refresh (momentum
+    transport) and whole trajectories on (2, 2), (1, 2) and (2, 4) grids against the same oracles."""
+    monkeypatch.setenv("SOAP_TP_PUSH_PRODUCTS", "1")
+    run_distributed(cases.case_batch, 4, "cuda", [
+        ("case_rotate", ((9, 13), 2, GRID4)), ("case_rotate", ((260, 390), 64, GRID4)),
+        ("case_refresh", ((200, 136), 64, GRID4)), ("case_soap_shared_basis", ((384, 256), 64, GRID4, 1, 6, 1e-5)),
+        ("case_soap_trajectory", ((20, 20), 2, GRID4, 1) + TINY)])
+    run_distributed(cases.case_batch, 2, "cuda", [("case_rotate", ((260, 390), 128, (1, 2))),
+                                                   ("case_soap_trajectory", ((12, 12), 2, (1, 2), 1) + TINY)])
+    run_distributed(cases.case_batch, 8, "cuda", [("case_rotate", ((520, 390), 64, (2, 4)))])
