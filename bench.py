@@ -253,6 +253,13 @@ def run(args: argparse.Namespace) -> int:
     # loop give the device time (the prefetched copy and the 4-byte read-back are under 1 % of its step).
     single_loop = args.impl == "reference"
     budget_seconds = float(os.environ.get("SOAP_TP_REFERENCE_BUDGET_SECONDS", "1200"))
+    # Everything allocated so far (modules, workspaces, caches) is permanent: keep the cyclic collector from walking
+    # it again in the middle of a launch-bound refresh step (both arms; a full collection of a process that has
+    # imported torch takes tens of milliseconds).
+    import gc
+
+    gc.collect()
+    gc.freeze()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -283,6 +290,8 @@ def run(args: argparse.Namespace) -> int:
         first = len(history) - args.steps
         steady_host = [t for i, t in enumerate(host_ms) if (first + i) % args.refresh_interval]
         summary["host_enqueue_ms_median_steady"] = round(statistics.median(steady_host), 3) if steady_host else None
+        refresh_host = [t for i, t in enumerate(host_ms) if (first + i) % args.refresh_interval == 0]
+        summary["host_enqueue_ms_refresh"] = round(sum(refresh_host) / len(refresh_host), 3) if refresh_host else None
         launches_timed = launches() - launches_before
         if args.impl == "ours" and args.stage_timing:
             stages = GLOBAL_STAGE_TIMER.summary()
@@ -333,12 +342,15 @@ def run(args: argparse.Namespace) -> int:
     loop_marks[0].record()
     prefetch(0)
     steps_done = 0
+    e2e_host_ms: list[float] = []
     for i in range(args.steps):
         slot = i % 2
         if i + 1 < args.steps:
             prefetch(i + 1)
         torch.cuda.current_stream().wait_event(arrived[slot])
+        host_begin, waited = time.perf_counter(), status_wait_seconds()
         update = step_fn(device_buffers[slot])
+        e2e_host_ms.append(round((time.perf_counter() - host_begin - (status_wait_seconds() - waited)) * 1e3, 3))
         consumed[slot].record()
         used[slot] = True
         metric_host[slot:slot + 1].copy_(torch.linalg.vector_norm(update).reshape(1), non_blocking=True)
@@ -456,6 +468,7 @@ def run(args: argparse.Namespace) -> int:
                 "h2d_bytes_per_step": shard_bytes,
                 "d2h_bytes_per_step": 4,
                 "step_ms": e2e_step_ms,
+                "host_ms_rank0": e2e_host_ms,     # host time inside each call (without the status-word wait)
             },
             "gpu_launches": int(launches_timed),
         }
