@@ -126,3 +126,19 @@ def test_push_products(monkeypatch):
     run_distributed(cases.case_batch, 2, "cuda", [("case_rotate", ((260, 390), 128, (1, 2))),
                                                    ("case_soap_trajectory", ((12, 12), 2, (1, 2), 1) + TINY)])
     run_distributed(cases.case_batch, 8, "cuda", [("case_rotate", ((520, 390), 64, (2, 4)))])
+
+
+def test_grids_that_are_not_powers_of_two():
+    """Three ranks as a (3, 1) grid and six ranks as a (2, 3) grid through the CUDA engine (the single-GPU QR's
+    leader/worker split then has groups of one and three ranks), small and multi-block shapes."""
+    def specs(grid):
+        return [("case_redistribute", ((12, 18), 2, grid, 0)), ("case_gram", ((12, 18), 2, grid, 1, 0.25)),
+                ("case_gram", ((384, 252), 64, grid, 0, 0.5)), ("case_rotate", ((12, 18), 2, grid)),
+                ("case_rotate", ((390, 264), 64, grid)), ("case_permute", ((18, 12), 4, grid)),
+                ("case_power_iteration_qr", (13, 2, grid)), ("case_power_iteration_qr", (700, 128, grid)),
+                ("case_initialize_basis", ((12, 18), "right", 2, grid, "eigh")), ("case_refresh", ((12, 18), 2, grid)),
+                ("case_refresh", ((390, 264), 64, grid)), ("case_soap_shared_basis", ((12, 18), 2, grid, 1, 5, 1e-5)),
+                ("case_soap_shared_basis", ((384, 252), 64, grid, 0, 5, 1e-5))]
+
+    run_distributed(cases.case_batch, 3, "cuda", specs((3, 1)))
+    run_distributed(cases.case_batch, 6, "cuda", specs((2, 3)))

@@ -69,3 +69,20 @@ def test_shared_basis_trajectory():
         ("case_soap_shared_basis", ((20, 20), 2, (2, 2), 1, 6, 1e-5)),
         ("case_soap_shared_basis", ((12, 16), 3, (2, 2), 0, 6, 1e-5)),
         ("case_soap_shared_basis", ((96, 64), 16, (2, 2), 1, 5, 1e-5))])
+
+
+ODD_GRID_SPECS = lambda grid, world: [
+    ("case_redistribute", ((12, 18), 2, grid, 0)), ("case_redistribute", ((18, 12), 4, grid, 1)),
+    ("case_gram", ((12, 18), 2, grid, 1, 0.25)), ("case_gram", ((18, 12), 4, grid, 0, 0.0)),
+    ("case_rotate", ((12, 18), 2, grid)), ("case_permute", ((18, 12), 4, grid)),
+    ("case_power_iteration_qr", (13, 2, grid)), ("case_initialize_basis", ((12, 18), "right", 2, grid, "eigh")),
+    ("case_refresh", ((12, 18), 2, grid)),
+    ("case_soap_shared_basis", ((12, 18), 2, grid, 1, 5, 1e-5)),
+]
+
+
+def test_grids_that_are_not_powers_of_two():
+    """Three ranks as a (3, 1) column of processes and six ranks as a (2, 3) grid: every rank class has a different
+    number of blocks and some ranks own ragged or empty edges."""
+    run_distributed(cases.case_batch, 3, "cpu", ODD_GRID_SPECS((3, 1), 3))
+    run_distributed(cases.case_batch, 6, "cpu", ODD_GRID_SPECS((2, 3), 6))
