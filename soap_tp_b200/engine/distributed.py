@@ -19,6 +19,7 @@ from __future__ import annotations
 import math
 import os
 import weakref
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Any, Dict, MutableMapping, Optional, Tuple
 
@@ -48,6 +49,9 @@ OVERLAP_GRAM = os.environ.get("SOAP_TP_OVERLAP_GRAM", "1") != "0"
 # over NVLink, in the part of a tile that no other work of its CTA overlaps; the pull kernel streams the same bytes
 # at 600-700 GB/s), and 11.35 against 11.34 ms on 2 GPUs.
 PUSH_PRODUCTS = os.environ.get("SOAP_TP_PUSH_PRODUCTS", "0") == "1"
+# Operand planes of the eigenbases kept per engine between steps (SOAP_TP_BASIS_CACHE_GB, default 40): beyond that the
+# least recently used ones are dropped and rebuilt on use, trading about a millisecond per step and basis for memory.
+BASIS_CACHE_BYTES = int(float(os.environ.get("SOAP_TP_BASIS_CACHE_GB", "40")) * 2**30)
 # output tiles a chunk must keep (about one wave of the 148 SMs); tests lower it to chunk small problems
 PIPELINE_MIN_TILES = max(1, int(os.environ.get("SOAP_TP_PIPELINE_MIN_TILES", "120")))
 
@@ -127,7 +131,7 @@ class GridEngine:
         self.world = self.comm.world
         self.pr, self.pc = grid_coords(self.rank, grid)
         self._planes: Dict[tuple, k.Planes] = {}
-        self._basis_cache: Dict[tuple, dict] = {}
+        self._basis_cache: "OrderedDict[tuple, dict]" = OrderedDict()
         self._leader_tables: Dict[tuple, Tensor] = {}
 
     # ---- small helpers -----------------------------------------------------------------------
@@ -196,7 +200,12 @@ class GridEngine:
     def basis_panels(self, Q: Tensor, size: int, tag: str) -> Tuple[k.Planes, k.Planes]:
         """Planes of ``Q[:, my column class]`` (depth = size) and of ``Q^T[:, my column class]``,
         i.e. rows of ``Q`` in my column class.  Collective; cached on the tensor version."""
-        entry = self._basis_cache.setdefault((Q.data_ptr(), size), {})
+        cache_key = (Q.data_ptr(), size)
+        entry = self._basis_cache.get(cache_key)
+        if entry is None:
+            entry = self._basis_cache[cache_key] = {}
+        else:
+            self._basis_cache.move_to_end(cache_key)
         # Ranks run the same program on the same step, so staleness is decided locally: a basis
         # changes on all ranks (refresh, initialisation, checkpoint load) or on none.  The entry belongs to one
         # tensor OBJECT: a new tensor that the allocator happens to place at the address of a freed one (with
@@ -212,8 +221,24 @@ class GridEngine:
         dist_gather(source, IDENTITY, self.col_map(), size, cols, planes=plain)
         dist_gather(source, IDENTITY, self.col_map(), size, cols, transpose=True, planes=transposed)
         self.comm.barrier()
-        entry.update(key=(Q._version, size), plain=plain, transposed=transposed, owner=weakref.ref(Q))
+        # 12 bytes per element of this rank's share of the basis (two orientations, value plane + low plane), counted
+        # with the widest rank's share so that every rank evicts the same entries
+        entry.update(key=(Q._version, size), plain=plain, transposed=transposed, owner=weakref.ref(Q),
+                     bytes=12 * size * numroc(size, self.nb, 0, self.Pc))
+        self._evict_basis_planes(keep=cache_key)
         return plain, transposed
+
+    def _evict_basis_planes(self, keep: tuple) -> None:
+        """Operand planes of the bases are three times the size of the bases themselves.  With many parameters (a
+        32-layer decoder) they are kept only up to ``BASIS_CACHE_BYTES`` per engine, least recently used first out;
+        an evicted basis is split again on its next use (one staging copy and two pulls per step)."""
+        total = sum(entry.get("bytes", 0) for entry in self._basis_cache.values())
+        for key in list(self._basis_cache):
+            if total <= BASIS_CACHE_BYTES:
+                break
+            if key == keep:
+                continue
+            total -= self._basis_cache.pop(key).get("bytes", 0)
 
     def side_stream(self) -> "torch.cuda.Stream":
         """The stream on which work that is independent of the rotations (the Gram EMAs) runs beside them."""

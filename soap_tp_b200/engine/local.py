@@ -60,10 +60,17 @@ class ParameterContext:
     def __init__(self) -> None:
         self.left = BasisPlanes()
         self.right = BasisPlanes()
+        self.bytes = 0
 
 
 _CONTEXTS: "OrderedDict[tuple, ParameterContext]" = OrderedDict()
 _WORKSPACES: Dict[tuple, Any] = {}
+
+
+# Operand planes of the eigenbases kept between steps (SOAP_TP_BASIS_CACHE_GB, default 40): 12 bytes per basis element
+# (two orientations, value plane + low plane), three times the bases themselves.  Beyond the limit the least recently
+# used parameters' planes are dropped and split again on use.
+BASIS_CACHE_BYTES = int(float(os.environ.get("SOAP_TP_BASIS_CACHE_GB", "40")) * 2**30)
 
 
 def context_for(state: MutableMapping[str, Any]) -> ParameterContext:
@@ -72,9 +79,17 @@ def context_for(state: MutableMapping[str, Any]) -> ParameterContext:
     ctx = _CONTEXTS.get(key)
     if ctx is None:
         ctx = ParameterContext()
+        rows, cols = state["momentum"].shape
+        ctx.bytes = 12 * (rows * rows + cols * cols)
         _CONTEXTS[key] = ctx
-        while len(_CONTEXTS) > 4096:
-            _CONTEXTS.popitem(last=False)
+    else:
+        _CONTEXTS.move_to_end(key)
+    total = sum(c.bytes for c in _CONTEXTS.values())
+    for other in list(_CONTEXTS):
+        if total <= BASIS_CACHE_BYTES and len(_CONTEXTS) <= 4096:
+            break
+        if other != key:
+            total -= _CONTEXTS.pop(other).bytes
     return ctx
 
 

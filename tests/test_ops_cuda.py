@@ -142,3 +142,13 @@ def test_grids_that_are_not_powers_of_two():
 
     run_distributed(cases.case_batch, 3, "cuda", specs((3, 1)))
     run_distributed(cases.case_batch, 6, "cuda", specs((2, 3)))
+
+
+def test_basis_planes_rebuilt_after_eviction(monkeypatch):
+    """With no room in the cache of basis planes every basis is split again on every use (the two bases of a
+    parameter evict each other): same trajectories on one GPU and on a (2, 2) grid."""
+    monkeypatch.setenv("SOAP_TP_BASIS_CACHE_GB", "0")
+    run_distributed(cases.case_batch, 1, "cuda", [("case_soap_shared_basis", ((384, 260), 64, (1, 1), 0, 5, 1e-5)),
+                                                   ("case_soap_trajectory", ((20, 20), 2, (1, 1), 1) + TINY)])
+    run_distributed(cases.case_batch, 4, "cuda", [("case_soap_shared_basis", ((384, 256), 64, GRID4, 1, 5, 1e-5)),
+                                                   ("case_soap_trajectory", ((20, 20), 2, GRID4, 1) + TINY)])

@@ -46,3 +46,23 @@ def test_poll_status_uses_the_device_word(monkeypatch):
     kernels.poll_status(device)
     with pytest.raises(kernels.SoapKernelError, match="accumulator"):
         kernels.poll_status(device)
+
+
+def test_basis_plane_cache_is_bounded(monkeypatch):
+    """The per-parameter caches of basis planes evict least-recently-used entries beyond a byte limit; the entry in
+    use always stays (host logic only: no planes are built here)."""
+    import torch
+
+    from soap_tp_b200.engine import local
+
+    monkeypatch.setattr(local, "BASIS_CACHE_BYTES", 12 * (64 * 64 + 32 * 32) * 2)      # room for two parameters
+    local._CONTEXTS.clear()
+    states = [dict(left_basis=torch.zeros(64, 64), right_basis=torch.zeros(32, 32), momentum=torch.zeros(64, 32))
+              for _ in range(4)]
+    contexts = [local.context_for(state) for state in states]
+    assert len(local._CONTEXTS) == 2 and local.context_for(states[3]) is contexts[3]
+    assert local.context_for(states[2]) is contexts[2]          # still cached, now the most recent
+    fresh = local.context_for(states[0])                         # evicted earlier: a new context, and 3 goes out
+    assert fresh is not contexts[0] and len(local._CONTEXTS) == 2
+    assert local.context_for(states[2]) is contexts[2]
+    local._CONTEXTS.clear()
