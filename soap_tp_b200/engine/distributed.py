@@ -230,14 +230,18 @@ class GridEngine:
 
     def _evict_basis_planes(self, keep: tuple) -> None:
         """Operand planes of the bases are three times the size of the bases themselves.  With many parameters (a
-        32-layer decoder) they are kept only up to ``BASIS_CACHE_BYTES`` per engine, least recently used first out;
-        an evicted basis is split again on its next use (one staging copy and two pulls per step)."""
+        32-layer decoder) they are kept only up to ``BASIS_CACHE_BYTES`` per engine; an evicted basis is split again
+        on its next use (one staging copy and two pulls per step).  Entries of tensors that no longer exist go
+        first; then the MOST recently used ones, because an optimizer walks its parameters in the same order every
+        step: the oldest entries are the next to be used, and dropping them would make every access miss."""
         total = sum(entry.get("bytes", 0) for entry in self._basis_cache.values())
-        for key in list(self._basis_cache):
+        if total <= BASIS_CACHE_BYTES:
+            return
+        dead = [key for key, entry in self._basis_cache.items()
+                if key != keep and (entry.get("owner") is None or entry["owner"]() is None)]
+        for key in dead + [key for key in reversed(self._basis_cache) if key != keep and key not in dead]:
             if total <= BASIS_CACHE_BYTES:
                 break
-            if key == keep:
-                continue
             total -= self._basis_cache.pop(key).get("bytes", 0)
 
     def side_stream(self) -> "torch.cuda.Stream":

@@ -69,7 +69,7 @@ _WORKSPACES: Dict[tuple, Any] = {}
 
 # Operand planes of the eigenbases kept between steps (SOAP_TP_BASIS_CACHE_GB, default 40): 12 bytes per basis element
 # (two orientations, value plane + low plane), three times the bases themselves.  Beyond the limit the least recently
-# used parameters' planes are dropped and split again on use.
+# used parameters' planes are dropped and split again on use (most recently used first, see ``context_for``).
 BASIS_CACHE_BYTES = int(float(os.environ.get("SOAP_TP_BASIS_CACHE_GB", "40")) * 2**30)
 
 
@@ -85,10 +85,14 @@ def context_for(state: MutableMapping[str, Any]) -> ParameterContext:
     else:
         _CONTEXTS.move_to_end(key)
     total = sum(c.bytes for c in _CONTEXTS.values())
-    for other in list(_CONTEXTS):
-        if total <= BASIS_CACHE_BYTES and len(_CONTEXTS) <= 4096:
-            break
-        if other != key:
+    if total > BASIS_CACHE_BYTES or len(_CONTEXTS) > 4096:
+        # contexts of tensors that no longer exist go first; then the MOST recently used ones: an optimizer walks
+        # its parameters in the same order every step, so the oldest contexts are the next to be used
+        dead = [other for other, c in _CONTEXTS.items()
+                if other != key and c.left.owner is not None and c.left.owner() is None]
+        for other in dead + [other for other in reversed(_CONTEXTS) if other != key and other not in dead]:
+            if total <= BASIS_CACHE_BYTES and len(_CONTEXTS) <= 4096:
+                break
             total -= _CONTEXTS.pop(other).bytes
     return ctx
 
