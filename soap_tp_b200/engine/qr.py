@@ -32,6 +32,10 @@ PANEL = _C.QR_PANEL_WIDTH
 # Two Householder columns per exchange step of the panel kernel where that is numerically safe
 # (SOAP_TP_QR_PAIR_STEPS=0: the one-column kernel).
 PAIR_STEPS = os.environ.get("SOAP_TP_QR_PAIR_STEPS", "1") != "0"
+# The reflectors of two consecutive panels reach the far columns (and the forward-accumulated Q^T) as ONE rank-256
+# update: half the passes over those matrices, which are what the updates cost (SOAP_TP_QR_AGGREGATE=0: one rank-128
+# update per panel).
+AGGREGATE = os.environ.get("SOAP_TP_QR_AGGREGATE", "1") != "0"
 _WORKSPACES: Dict[tuple, dict] = {}
 
 
@@ -57,7 +61,16 @@ def _workspace(n: int, device, slot: int = 0) -> dict:
             "partials_q": torch.empty(16 * PANEL * n, dtype=torch.float32, device=device),
             "Zq": k.Planes.empty(PANEL, n, device), "Wq": k.Planes.empty(PANEL, n, device),
             "staging": torch.empty((n, n), dtype=torch.float32, device=device).T,
+            # reflectors of two consecutive panels applied as one rank-256 update (see `_pair_reflector`); the set
+            # with the suffix "q" serves the forward accumulation of Q on its own stream
+            "zero_block": torch.zeros((PANEL, PANEL), dtype=torch.float32, device=device),
         }
+        for suffix in ("", "q"):
+            ws["Z2" + suffix] = k.Planes.empty(2 * PANEL, n, device)
+            ws["W2" + suffix] = k.Planes.empty(2 * PANEL, n, device)
+            ws["partials2" + suffix] = torch.empty(16 * 2 * PANEL * n, dtype=torch.float32, device=device)
+            for name in ("S2", "Y2", "A2"):
+                ws[name + suffix] = k.Planes.empty(PANEL, PANEL, device)
         _WORKSPACES[key] = ws
     return ws
 
@@ -156,6 +169,46 @@ def _q_stream(device, slot: int) -> "torch.cuda.Stream":
     if key not in _PANEL_STREAMS:
         _PANEL_STREAMS[key] = torch.cuda.Stream(device=device)
     return _PANEL_STREAMS[key]
+
+
+def _pair_reflector(ws: dict, V: k.Planes, a: int, n: int, suffix: str = "", backward: bool = False) -> tuple:
+    """``(V2, Z2)`` for the reflectors of two full-width panels ``a``, ``b = a + 1`` taken together:
+    ``H_a H_b = I - V2 T2 V2^T`` with ``V2 = [V_a, V_b]`` (the window of the reflector planes that starts at panel
+    ``a``; the caller has zeroed the 128 rows of ``V_b``'s columns above its own first row) and
+    ``T2 = [[T_a, T_ab], [0, T_b]]``, ``T_ab = -T_a (V_a^T V_b) T_b``.
+
+    Forward (trailing matrix, forward accumulation of ``Q^T``): ``Z2 = T2 V2^T = [[Z_a + T_ab V_b^T], [0, Z_b]]`` and
+    ``C -= Z2^T (V2^T C)`` applies ``(H_a H_b)^T`` in one pass over ``C``.  ``backward`` (explicit ``Q`` from the
+    identity, last panel first): ``Z2 = T2^T V2^T = [[T_a^T V_a^T], [T_ab^T V_a^T + [0, T_b^T V_b^T]]]`` and
+    ``Q -= Z2^T (V2^T Q)`` applies ``H_a H_b``.  Seven small products either way; ``suffix`` selects the scratch set
+    (the forward accumulation of ``Q`` runs on its own stream).
+    """
+    ja = a * PANEL
+    jb, ra = ja + PANEL, n - ja
+    rb = ra - PANEL
+    b = a + 1
+    planes_of = lambda t: k.Planes(t.hi, t.lo, PANEL, PANEL, t.ld)
+    T_a, Tt_a, T_b, Tt_b = (planes_of(ws[name][i]) for name, i in (("T", a), ("Tt", a), ("T", b), ("Tt", b)))
+    vt_a, vt_b = ws["Vt"][a].sub(0, 0, PANEL, ra), ws["Vt"][b].sub(0, 0, PANEL, rb)
+    S, Y, A, Z2 = ws["S2" + suffix], ws["Y2" + suffix], ws["A2" + suffix], ws["Z2" + suffix]
+    va_low, vb = V.sub(jb, ja, rb, PANEL), V.sub(jb, jb, rb, PANEL)
+    small = dict(mode=k.EPI_SPLIT, force_narrow=True)
+    if backward:
+        _skinny_product(ws, vb, va_low, S, scratch="partials2" + suffix)                # S^T = V_b^T V_a
+        k.gemm(S, T_b, out_planes=Y, **small)                                            # S T_b
+        k.gemm(Tt_a, Y, out_planes=A, alpha=-1.0, **small)                               # T_ab = -T_a (S T_b)
+        k.gemm(T_a, vt_a, out_planes=Z2.sub(0, 0, PANEL, ra), **small)                   # T_a^T V_a^T
+        k.gemm(A, vt_a, out_planes=Z2.sub(PANEL, 0, PANEL, ra), **small)                 # T_ab^T V_a^T
+        k.gemm(T_b, vt_b, out_planes=Z2.sub(PANEL, PANEL, PANEL, rb), beta=1.0, **small)   # + T_b^T V_b^T
+    else:
+        _skinny_product(ws, va_low, vb, S, scratch="partials2" + suffix)                # S = V_a^T V_b
+        k.gemm(S, Tt_a, out_planes=Y, **small)                                           # S^T T_a^T
+        k.gemm(T_b, Y, out_planes=A, alpha=-1.0, **small)                                # T_ab^T = -T_b^T S^T T_a^T
+        k.gemm(Tt_a, vt_a, out_planes=Z2.sub(0, 0, PANEL, ra), **small)                  # Z_a
+        k.gemm(A, vt_b, out_planes=Z2.sub(0, PANEL, PANEL, rb), beta=1.0, **small)       # + T_ab V_b^T
+        k.split_planes(ws["zero_block"], out=Z2.sub(PANEL, 0, PANEL, PANEL))
+        k.gemm(Tt_b, vt_b, out_planes=Z2.sub(PANEL, PANEL, PANEL, rb), **small)          # Z_b
+    return V.sub(ja, ja, ra, 2 * PANEL), Z2.sub(0, 0, 2 * PANEL, ra)
 
 
 def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_order: Optional[Tensor], slot: int,
@@ -257,11 +310,45 @@ def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_o
             w = ws["Wq"].sub(0, 0, bw, n) if bw == PANEL else k.Planes.empty(bw, n, device)
             _skinny_product(ws, v, block, w, scratch="partials_q")                                # W = V^T Q^T
             k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0)                 # Q^T -= Z^T W
+    def paired(p: int) -> bool:
+        """Panel ``p`` (even) hands its far updates over to a rank-256 update together with panel ``p + 1``."""
+        return AGGREGATE and p % 2 == 0 and p + 1 < len(panels) and n - panels[p + 1] >= PANEL
+
+    def far_update(p: int, first_col: int, count: int) -> None:
+        """The reflector of panel ``p`` for the columns beyond the next panel."""
+        if p % 2 == 1 and paired(p - 1):
+            # both panels' reflectors in one pass over these columns (they have seen neither)
+            ja = panels[p - 1]
+            v2, z2 = _pair_reflector(ws, V, p - 1, n)
+            w2 = ws["W2"].sub(0, 0, 2 * PANEL, count)
+            block = C.sub(ja, first_col, n - ja, count)
+            _skinny_product(ws, v2, block, w2, scratch="partials2")
+            k.gemm(z2, w2, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0)
+        elif paired(p):
+            update(p, first_col, min(PANEL, count))    # only the panel after next, which is factored before the pair update
+        else:
+            update(p, first_col, count)
+
+    def accumulate_q_pair(p: int, after: "torch.cuda.Event") -> None:
+        """``Q^T <- (H_{p-1} H_p)^T Q^T`` in one pass (forward accumulation, own stream and scratch)."""
+        ja = panels[p - 1]
+        q_stream.wait_event(after)
+        with torch.cuda.stream(q_stream):
+            v2, z2 = _pair_reflector(ws, V, p - 1, n, suffix="q")
+            block = Qp.sub(ja, 0, n - ja, n)
+            w2 = ws["W2q"].sub(0, 0, 2 * PANEL, n)
+            _skinny_product(ws, v2, block, w2, scratch="partials2q")
+            k.gemm(z2, w2, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0)
+
     for p, j0 in enumerate(panels):
         bw, r = min(PANEL, n - j0), n - j0
         nc = n - j0 - bw
         main.wait_event(done)
         panel_done = done
+        if paired(p):
+            # rows of the next panel's reflector columns above its own first row: zero, so that the two panels'
+            # reflectors can be used as one 256-column operand (nothing else ever writes there)
+            k.split_planes(ws["zero_block"], out=V.sub(j0, j0 + PANEL, PANEL, PANEL))
         if nc > 0 or publisher is not None:
             vt, Tt = ws["Vt"][p], ws["Tt"][p]
             t_op = k.Planes(Tt.hi, Tt.lo, bw, bw, Tt.ld)
@@ -276,9 +363,12 @@ def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_o
             ready.record(main)
             done = launch_panel(p + 1, ready)
             if nc > ahead:
-                update(p, j0 + bw + ahead, nc - ahead)
+                far_update(p, j0 + bw + ahead, nc - ahead)
         if forward_q:
-            accumulate_q(p, panel_done)
+            if p % 2 == 1 and paired(p - 1):
+                accumulate_q_pair(p, panel_done)
+            elif not paired(p):
+                accumulate_q(p, panel_done)
         yield
     if publisher is not None:
         return
@@ -299,15 +389,23 @@ def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_o
     for p in reversed(range(len(panels))):
         j0 = panels[p]
         bw, r = min(PANEL, n - j0), n - j0
+        if p % 2 == 1 and paired(p - 1):
+            continue                                     # applied together with panel p - 1
+        block = Qp.sub(j0, j0, r, r)
+        if paired(p):
+            v2, z2 = _pair_reflector(ws, V, p, n, backward=True)
+            w2 = ws["W2"].sub(0, 0, 2 * PANEL, r)
+            _skinny_product(ws, v2, block, w2, scratch="partials2")                         # W = [V_a V_b]^T Q
+            k.gemm(z2, w2, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0,
+                   out=Q if p == 0 else None)                                               # Q -= Z2^T W
+            continue
         v, vt, T = V.sub(j0, j0, r, bw), ws["Vt"][p], ws["T"][p]
         t_op = k.Planes(T.hi, T.lo, bw, bw, T.ld)
         vt_op = vt.sub(0, 0, bw, r)
         z = ws["Z"].sub(0, 0, bw, r) if bw == PANEL else k.Planes.empty(bw, r, device)
         k.gemm(t_op, vt_op, mode=k.EPI_SPLIT, out_planes=z, force_narrow=True)                # Z = T^T V^T
-        block = Qp.sub(j0, j0, r, r)
         w = ws["W"].sub(0, 0, bw, r) if bw == PANEL else k.Planes.empty(bw, r, device)
         _skinny_product(ws, v, block, w)                                                    # W = V^T Q
         k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0,
                out=Q if p == 0 else None)                                                   # Q -= Z^T W
-        yield
     k.mark_written(Q)
