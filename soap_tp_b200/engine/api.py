@@ -11,7 +11,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from ..layout import empty_2d_block_cyclic_like_shape, local_2d_block_cyclic_shape
+from ..layout import empty_2d_block_cyclic_like_shape
 from . import kernels as k
 from . import local
 

@@ -23,7 +23,7 @@ because kernels that wait for one another must not be separate launches on one d
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 import torch.distributed as dist

@@ -7,10 +7,7 @@ from __future__ import annotations
 
 from typing import Optional
 
-import torch
 from torch import Tensor
-
-from . import kernels as k
 
 
 def householder_qr(matrix: Tensor, Q: Tensor, column_order: Optional[Tensor] = None) -> Tensor:

@@ -26,7 +26,6 @@ on the padded diagonal: the padding never couples to the true block and sorts to
 """
 from __future__ import annotations
 
-import math
 from typing import Dict
 
 import torch

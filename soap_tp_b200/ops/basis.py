@@ -20,7 +20,7 @@ broadcast, as ``"eigh"`` does in the reference.
 """
 from __future__ import annotations
 
-from typing import Any, Literal, Optional, Tuple
+from typing import Any, Optional, Tuple
 
 import torch
 import torch.distributed as dist

@@ -14,7 +14,7 @@ no pack, no unpack and no intermediate message.  CPU tensors use the dense host 
 """
 from __future__ import annotations
 
-from typing import Literal, Optional, Tuple
+from typing import Literal, Tuple
 
 import torch
 import torch.distributed as dist

@@ -25,7 +25,6 @@ on; ``load_state_dict()`` checks it and restores fp32 column-major buffers bit-e
 """
 from __future__ import annotations
 
-import math
 from typing import Any, Dict, Iterable, Optional, Tuple
 
 import torch
@@ -33,7 +32,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from .layout import allocate_2d_block_cyclic, most_square_grid
-from .step import STATE_BUFFER_NAMES, soap_step, state_shapes
+from .step import soap_step, state_shapes
 
 
 class SoapTP(torch.optim.Optimizer):

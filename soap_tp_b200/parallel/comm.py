@@ -18,13 +18,12 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from ..layout import Grid, validate_process_grid
 
 
 from ..engine.kernels import SoapCommTimeout  # noqa: E402  (re-exported: a bounded device-side wait on a peer ran out)
