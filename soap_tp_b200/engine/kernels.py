@@ -10,7 +10,7 @@ from __future__ import annotations
 import math
 import os
 import time
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, Optional
 
 import torch
@@ -188,6 +188,9 @@ class Planes:
     ld: int
     hl: Optional[Tensor] = None
     ld16: int = 0
+    # windows handed out by `sub` (a launch-heavy driver asks for the same few thousand windows at every refresh, and
+    # slicing tensors is what its launching thread would otherwise spend its time on)
+    _windows: Dict[tuple, "Planes"] = field(default_factory=dict, repr=False, compare=False)
 
     @property
     def mixed(self) -> bool:
@@ -206,13 +209,22 @@ class Planes:
 
     def sub(self, k0: int, c0: int, depth: int, cols: int) -> "Planes":
         """Operand planes of the sub-matrix starting at row ``k0`` (a multiple of 4; of 32 for mixed planes, whose
-        depth may only be shortened to a multiple of 32), column ``c0``."""
+        depth may only be shortened to a multiple of 32), column ``c0``.  Windows are cached: treat them as
+        read-only descriptions of the parent's memory."""
+        key = (k0, c0, depth, cols)
+        window = self._windows.get(key)
+        if window is not None:
+            return window
         assert k0 + depth <= self.ld and c0 + cols <= self.hi.shape[0]
         if self.mixed:
             assert k0 % 32 == 0 and (k0 + depth == self.depth or depth % 32 == 0)
-            return Planes(self.hi[c0:, k0:], None, depth, cols, self.ld, self.hl[c0:, 2 * k0:], self.ld16)
-        assert k0 % 4 == 0
-        return Planes(self.hi[c0:, k0:], self.lo[c0:, k0:], depth, cols, self.ld)
+            window = Planes(self.hi[c0:, k0:], None, depth, cols, self.ld, self.hl[c0:, 2 * k0:], self.ld16)
+        else:
+            assert k0 % 4 == 0
+            window = Planes(self.hi[c0:, k0:], self.lo[c0:, k0:], depth, cols, self.ld)
+        if len(self._windows) < 65536:
+            self._windows[key] = window
+        return window
 
     def low_pointers(self) -> dict:
         """Pointer arguments of the low part for the native calls."""

@@ -237,6 +237,7 @@ def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_o
     panels = list(range(0, n, PANEL))
     main = torch.cuda.current_stream(device)
     side = _panel_stream(device, slot) if os.environ.get("SOAP_TP_QR_LOOKAHEAD", "1") != "0" else main
+    status_pointer = k.status_word(device).data_ptr()
 
     def launch_panel(p: int, after: "torch.cuda.Event") -> "torch.cuda.Event":
         """Panel ``p`` on the panel stream, once ``after`` has happened; returns its completion event."""
@@ -246,19 +247,20 @@ def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_o
         tau = ws["tau"][j0:]
         T, Tt = ws["T"][p], ws["Tt"][p]
         side.wait_event(after)
-        with torch.cuda.stream(side):
-            arguments = (panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(),
-                         v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(),
-                         T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
-                         k.status_word(device).data_ptr(), stream())
-            if PAIR_STEPS:
-                # 256-row CTAs: measured faster than (2048 rows and up) or within 2 % of (1024 rows) 128-row CTAs
-                _C.qr_panel_pairs(*arguments, 256)
-            else:
-                _C.qr_panel(*arguments)
-            k._count("qr_panel_kernel")
-            done = torch.cuda.Event()
-            done.record(side)
+        # launched on the panel stream by its handle (entering a stream context costs the launching thread more
+        # than the launch itself)
+        arguments = (panel.hi.data_ptr(), panel.lo.data_ptr(), panel.ld, r, bw, v.hi.data_ptr(), v.lo.data_ptr(),
+                     v.ld, vt.hi.data_ptr(), vt.lo.data_ptr(), vt.ld, tau.data_ptr(), T.hi.data_ptr(),
+                     T.lo.data_ptr(), Tt.hi.data_ptr(), Tt.lo.data_ptr(), T.ld, ws["exchange"].data_ptr(),
+                     status_pointer, side.cuda_stream)
+        if PAIR_STEPS:
+            # 256-row CTAs: measured faster than (2048 rows and up) or within 2 % of (1024 rows) 128-row CTAs
+            _C.qr_panel_pairs(*arguments, 256)
+        else:
+            _C.qr_panel(*arguments)
+        k._count("qr_panel_kernel")
+        done = torch.cuda.Event()
+        done.record(side)
         return done
 
     def z_of(p: int) -> k.Planes:
@@ -310,9 +312,14 @@ def _factorisation_steps(matrix: Optional[Tensor], Q: Optional[Tensor], column_o
             w = ws["Wq"].sub(0, 0, bw, n) if bw == PANEL else k.Planes.empty(bw, n, device)
             _skinny_product(ws, v, block, w, scratch="partials_q")                                # W = V^T Q^T
             k.gemm(z, w, mode=k.EPI_SPLIT, out_planes=block, alpha=-1.0, beta=1.0)                 # Q^T -= Z^T W
+    # A leader that publishes its reflectors to worker ranks keeps one update per panel: its factorisation is bound by
+    # the chain of panels (and, with eight processes on one host, by its launching thread), so the pair update's
+    # dozen extra small launches per pair buy nothing there (8192 on 4 GPUs: refresh.qr 3.29 against 3.26-3.35 ms/step).
+    aggregate = AGGREGATE and publisher is None
+
     def paired(p: int) -> bool:
         """Panel ``p`` (even) hands its far updates over to a rank-256 update together with panel ``p + 1``."""
-        return AGGREGATE and p % 2 == 0 and p + 1 < len(panels) and n - panels[p + 1] >= PANEL
+        return aggregate and p % 2 == 0 and p + 1 < len(panels) and n - panels[p + 1] >= PANEL
 
     def far_update(p: int, first_col: int, count: int) -> None:
         """The reflector of panel ``p`` for the columns beyond the next panel."""
