@@ -70,3 +70,45 @@ def test_basis_plane_cache_is_bounded(monkeypatch):
             hits += any(local.context_for(state) is ctx for ctx in resident)
         assert hits >= 1 and len(local._CONTEXTS) == 2
     local._CONTEXTS.clear()
+
+
+def test_grid_engine_evicts_dead_then_most_recent_basis_planes(monkeypatch):
+    """Eviction in the multi-GPU engine depends only on the order of use and on rank-independent sizes, so every
+    rank drops the same entries: entries of tensors that no longer exist first, then the most recently used."""
+    import weakref
+    from collections import OrderedDict
+
+    import torch
+
+    from soap_tp_b200.engine import distributed
+
+    monkeypatch.setattr(distributed, "BASIS_CACHE_BYTES", 250)
+    engine = object.__new__(distributed.GridEngine)
+    engine._basis_cache = OrderedDict()
+    alive = [torch.zeros(1) for _ in range(4)]
+    gone = torch.zeros(1)
+    engine._basis_cache[("gone", 1)] = dict(bytes=100, owner=weakref.ref(gone))
+    del gone
+    for index, tensor in enumerate(alive):
+        engine._basis_cache[(index, 1)] = dict(bytes=100, owner=weakref.ref(tensor))
+    engine._evict_basis_planes(keep=(3, 1))
+    # 500 bytes -> the dead entry, then the most recently used ones other than the one in use, until 250 fit
+    assert list(engine._basis_cache) == [(0, 1), (3, 1)]
+    engine._evict_basis_planes(keep=(3, 1))
+    assert list(engine._basis_cache) == [(0, 1), (3, 1)]
+
+
+def test_windows_of_operand_planes_are_cached_views():
+    import torch
+
+    from soap_tp_b200.engine.kernels import Planes
+
+    hi, lo = torch.arange(48.0).reshape(6, 8), torch.zeros(6, 8)
+    planes = Planes(hi, lo, 8, 6, 8)
+    window = planes.sub(4, 2, 4, 3)
+    assert planes.sub(4, 2, 4, 3) is window and planes.sub(4, 2, 4, 2) is not window
+    assert window.depth == 4 and window.cols == 3 and window.ld == 8
+    assert window.hi.data_ptr() == hi[2:, 4:].data_ptr() and float(window.hi[0, 0]) == float(hi[2, 4])
+    hi[2, 4] = -1.0                                   # a window is a view: it sees what is written to the parent
+    assert float(window.hi[0, 0]) == -1.0
+    assert window.dense().shape == (4, 3)
